@@ -39,6 +39,21 @@ class CacheView:
     writable: bool           # False when the run reads the cache another run wrote
     kind: str = "full"
 
+    def tensors(self):
+        """The device tensors of this view, in a fixed order (what a replayed layer's pointers are moved between)."""
+        return [self.k, self.v]
+
+
+@dataclass
+class LatentView:
+    """What one run of a latent-attention mixer sees: one row per token for all heads."""
+    kv: torch.Tensor         # [pages, PAGE, width]
+    writable: bool
+    kind: str = "latent"
+
+    def tensors(self):
+        return [self.kv]
+
 
 class CacheStorage:
     """What a storage class must offer.  One object serves all runs with the same :class:`CacheNeed`.
@@ -86,6 +101,27 @@ class CacheGroup(CacheStorage):
     @property
     def nbytes(self) -> int:
         return 2 * self.k.numel() * self.k.element_size()
+
+
+@CACHE_KINDS.register("latent")
+class LatentGroup(CacheStorage):
+    """One row of ``need.dh`` values per position (a compressed latent and whatever travels with it), shared by
+    all heads, in the pages of the common pool."""
+
+    def __init__(self, need: CacheNeed, runs: List[int], *, n_pages: int, max_slots: int, max_context: int,
+                 dtype, device):
+        super().__init__(need, runs, n_pages=n_pages, max_slots=max_slots, max_context=max_context, dtype=dtype,
+                         device=device)
+        if need.nkvh != 1:
+            raise CacheError(f"a latent cache holds one row per token, not {need.nkvh}")
+        self.kv = torch.zeros((len(runs), n_pages, PAGE, need.dh), dtype=dtype, device=device)
+
+    def view(self, index: int, writable: bool) -> LatentView:
+        return LatentView(self.kv[index], writable=writable, kind=self.need.kind)
+
+    @property
+    def nbytes(self) -> int:
+        return self.kv.numel() * self.kv.element_size()
 
 
 class Cache:

@@ -1,3 +1,4 @@
 from .llama import LlamaMeta
+from .salepel import SalepelMeta
 from .registry import (Architecture, ConfigError, architecture_for, register_architecture,
                        registered_architectures, unregister_architecture)

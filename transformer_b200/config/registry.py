@@ -5,7 +5,7 @@ An :class:`Architecture` bundles four things and nothing else knows which model 
 * ``config_cls.from_dict``   -- typed configuration from the keys of ``config.json``
 * ``build_spec(config)``     -- the model as data: layers made of parts, and the order they run in
 * ``tensor_plan(config)``    -- which file tensor (by name) fills which parameter of which part
-* ``names``                  -- the strings ``config.json`` may carry in ``model_type`` /
+* ``names``                  -- the strings ``config.json`` may carry in ``model_type`` / ``architecture`` /
                                 ``architectures`` / ``general.architecture``
 
 The reference has no such table: each model is a crate of its own and the only dispatch on the
@@ -59,7 +59,7 @@ def registered_architectures() -> Iterable[str]:
 def architecture_names_in(config: Mapping[str, Any]) -> list:
     """Every string of a config.json that may name the architecture, most specific first."""
     found = []
-    for key in ("general.architecture", "model_type"):
+    for key in ("general.architecture", "model_type", "architecture"):
         v = config.get(key)
         if isinstance(v, str):
             found.append(v)
@@ -76,7 +76,7 @@ def architecture_for(config: Mapping[str, Any]) -> Architecture:
     if not names:
         raise ConfigError(
             "config.json names no architecture: expected one of the keys "
-            "'model_type', 'architectures' or 'general.architecture'"
+            "'model_type', 'architecture', 'architectures' or 'general.architecture'"
         )
     for n in names:
         arch = _ARCHITECTURES.get(n.lower())

@@ -120,6 +120,26 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
     *reinterpret_cast<uint4*>(p) = v;
 }
 
+// ---- gated activations of a feed-forward's (gate, up) pair ------------------------------------------
+// kind 0: silu(g) * u.   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha g') * (u' + 1).
+struct GluRule {
+    int kind;
+    float alpha, limit;
+};
+__device__ __forceinline__ float glu_apply(float g, float u, const GluRule r) {
+    if (r.kind == 0) return g / (1.0f + expf(-g)) * u;
+    g = fminf(g, r.limit);
+    u = fminf(fmaxf(u, -r.limit), r.limit);
+    return g / (1.0f + expf(-r.alpha * g)) * (u + 1.0f);
+}
+// the same with the hardware's exponential and division (2 ulp), for results that are rounded to bfloat16 next
+__device__ __forceinline__ float glu_apply_fast(float g, float u, const GluRule r) {
+    if (r.kind == 0) return __fdividef(g * u, 1.0f + __expf(-g));
+    g = fminf(g, r.limit);
+    u = fminf(fmaxf(u, -r.limit), r.limit);
+    return __fdividef(g * (u + 1.0f), 1.0f + __expf(-r.alpha * g));
+}
+
 // ---- launches with programmatic dependent launch ------------------------------------------------
 // Every kernel of this package begins with pdl_sync(): it lets the next kernel in the stream start
 // launching (its blocks become resident and wait), then waits until the previous kernel has finished

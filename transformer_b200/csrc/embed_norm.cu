@@ -7,12 +7,12 @@
 // x[i, :] = table[tokens[i], :]   (models/llama/cuda/src/infer.rs:98-104 copies row by row)
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                             float* __restrict__ x, int d) {
+                             float* __restrict__ x, int d, float scale) {
     pdl_sync();
     const int i = blockIdx.x;
     const T* src = table + (size_t)tokens[i] * d;
     float* dst = x + (size_t)i * d;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = ldf(src + c);
+    for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = ldf(src + c) * scale;
 }
 
 // Row r = rows ? rows[i] : i.
@@ -211,7 +211,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
 
 template <typename T>
 __global__ void embed_vec_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ x,
-                                 int d) {
+                                 int d, float scale) {
     pdl_sync();
     const int i = blockIdx.x;
     const T* src = table + (size_t)tokens[i] * d;
@@ -219,18 +219,84 @@ __global__ void embed_vec_kernel(const int* __restrict__ tokens, const T* __rest
     for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
         float f[8];
         load8(src + c, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= scale;      // a multiplication by one changes nothing
         store8(dst + c, f);
     }
 }
 
+
+// A block whose parts are normed AFTER they ran as well (x <- x + N_b(part(N_a(x)))) leaves this to the norm that
+// follows it.  Row r = rows ? rows[i] : i:
+//   u    = delta(r)                                         a part's output (or the experts' weighted sum, as above)
+//   v    = x[r] + u / sqrt(mean(u^2) + post_eps) * post_w   both statistics and the sum in float
+//   if (!rows) x[r] = v
+//   if (y) y[i] = v / sqrt(mean(v^2) + eps) * w             one rounding to T
+// The row lives in shared memory (d floats) between the passes.
 template <typename T>
-static int embed_launch(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
+__global__ void __launch_bounds__(256)
+post_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ wy,
+                        const int* __restrict__ pair_row, const float* __restrict__ topk_w, int k,
+                        const float* __restrict__ post_w, float post_eps, const int* __restrict__ rows,
+                        const float* __restrict__ w, float eps, T* __restrict__ y, int d) {
+    pdl_sync();
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* xr = x + (size_t)r * d;
+    const T* dr = delta ? delta + (size_t)r * d : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float u;
+        if (dr) {
+            u = ldf(dr + c);
+        } else {
+            u = 0.f;
+            for (int j = 0; j < k; ++j)
+                u += topk_w[(size_t)r * k + j] * ldf(wy + (size_t)pair_row[(size_t)r * k + j] * d + c);
+        }
+        row[c] = u;
+        ss += u * u;
+    }
+    ss = block_sum(ss, red);
+    const float rs1 = 1.0f / sqrtf(ss / (float)d + post_eps);
+    float ss2 = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float v = xr[c] + row[c] * rs1 * post_w[c];
+        if (!rows) xr[c] = v;
+        row[c] = v;
+        ss2 += v * v;
+    }
+    if (!y) return;
+    ss2 = block_sum(ss2, red);
+    const float rs2 = 1.0f / sqrtf(ss2 / (float)d + eps);
+    T* yr = y + (size_t)i * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) stf(yr + c, row[c] * rs2 * w[c]);
+}
+
+template <typename T>
+static int post_add_rmsnorm_launch(float* x, const void* delta, const void* wy, const int* pair_row,
+                                   const float* topk_w, int k, const float* post_w, float post_eps, const int* rows,
+                                   const float* w, float eps, void* y, int n_out, int d, cudaStream_t s) {
+    if (n_out < 0 || d <= 0 || !post_w || (y && !w)) return TB_ERR_ARG;
+    if ((delta == nullptr) == (wy == nullptr)) return TB_ERR_ARG;
+    if (wy && (!pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
+    if ((size_t)d * sizeof(float) > 48 * 1024) return TB_ERR_UNSUPPORTED;
+    if (n_out == 0) return 0;
+    TB_LAUNCH((post_add_rmsnorm_kernel<T>), n_out, 256, (size_t)d * sizeof(float), s, x, (const T*)delta, (const T*)wy,
+              pair_row, topk_w, k, post_w, post_eps, rows, w, eps, (T*)y, d);
+    return tb_last_error();
+}
+
+template <typename T>
+static int embed_launch(const int* tokens, const void* table, float* x, int nt, int d, float scale, cudaStream_t s) {
     if (nt < 0 || d <= 0) return TB_ERR_ARG;
     if (nt == 0) return 0;
     if (d % 8 == 0)
-        TB_LAUNCH((embed_vec_kernel<T>), nt, 128, 0, s, tokens, (const T*)table, x, d);
+        TB_LAUNCH((embed_vec_kernel<T>), nt, 128, 0, s, tokens, (const T*)table, x, d, scale);
     else
-        TB_LAUNCH((embed_kernel<T>), nt, 256, 0, s, tokens, (const T*)table, x, d);
+        TB_LAUNCH((embed_kernel<T>), nt, 256, 0, s, tokens, (const T*)table, x, d, scale);
     return tb_last_error();
 }
 template <typename T>
@@ -270,10 +336,30 @@ static int add_rmsnorm_launch(float* x, const void* delta, const void* wy, const
 
 extern "C" {
 int tb_embed_f32(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
-    return embed_launch<float>(tokens, table, x, nt, d, s);
+    return embed_launch<float>(tokens, table, x, nt, d, 1.0f, s);
+}
+// x[i] = table[tokens[i]] * scale, the product in float
+int tb_embed_scaled_f32(const int* tokens, const void* table, float* x, int nt, int d, float scale, cudaStream_t s) {
+    return embed_launch<float>(tokens, table, x, nt, d, scale, s);
+}
+int tb_embed_scaled_bf16(const int* tokens, const void* table, float* x, int nt, int d, float scale, cudaStream_t s) {
+    return embed_launch<__nv_bfloat16>(tokens, table, x, nt, d, scale, s);
 }
 int tb_embed_bf16(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
-    return embed_launch<__nv_bfloat16>(tokens, table, x, nt, d, s);
+    return embed_launch<__nv_bfloat16>(tokens, table, x, nt, d, 1.0f, s);
+}
+// x += norm(delta; post_w, post_eps), then y = norm(x; w, eps) (y may be null: the sum alone)
+int tb_post_add_rmsnorm_f32(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w,
+                            int k, const float* post_w, float post_eps, const int* rows, const float* w, float eps,
+                            void* y, int n_out, int d, cudaStream_t s) {
+    return post_add_rmsnorm_launch<float>(x, delta, wy, pair_row, topk_w, k, post_w, post_eps, rows, w, eps, y, n_out,
+                                          d, s);
+}
+int tb_post_add_rmsnorm_bf16(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w,
+                             int k, const float* post_w, float post_eps, const int* rows, const float* w, float eps,
+                             void* y, int n_out, int d, cudaStream_t s) {
+    return post_add_rmsnorm_launch<__nv_bfloat16>(x, delta, wy, pair_row, topk_w, k, post_w, post_eps, rows, w, eps,
+                                                  y, n_out, d, s);
 }
 // warm / warm_bytes: weights that the next kernel reads first, to be asked into L2 meanwhile (or null / 0).
 int tb_add_rmsnorm_f32(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w, int k,
@@ -311,6 +397,10 @@ int tb_add_rmsnorm_router_bf16(float* x, const void* delta, const void* wy, cons
 #include "tape.h"
 TB_TAPE_REGISTER(tb_embed_f32)
 TB_TAPE_REGISTER(tb_embed_bf16)
+TB_TAPE_REGISTER(tb_embed_scaled_f32)
+TB_TAPE_REGISTER(tb_embed_scaled_bf16)
+TB_TAPE_REGISTER(tb_post_add_rmsnorm_f32)
+TB_TAPE_REGISTER(tb_post_add_rmsnorm_bf16)
 TB_TAPE_REGISTER(tb_add_rmsnorm_f32)
 TB_TAPE_REGISTER(tb_add_rmsnorm_bf16)
 TB_TAPE_REGISTER(tb_add_rmsnorm_router_f32)

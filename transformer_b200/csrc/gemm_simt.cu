@@ -23,6 +23,9 @@ struct GemmArgs {
     long long b_group_stride;   // elements between B[g] and B[g+1]
     int lda, ldb, ldc;
     int M, N, K, G;
+    GluRule glu;                // DUAL: how the (gate, up) pair becomes one value
+    long long a_batch_stride;   // blockIdx.z = batch: elements between the batches' A, B (b_group_stride) and C;
+    long long c_batch_stride;   // zero without batches
 };
 
 #define GB_N 64
@@ -58,7 +61,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmArgs a) {
         if (row0 >= a.M) return;
     }
     const int n0 = blockIdx.y * GB_N;
-    const T* A = static_cast<const T*>(a.A);
+    if (gridDim.z > 1) g = blockIdx.z;      // batches: every batch has a matrix of its own and all the rows
+    const T* A = static_cast<const T*>(a.A) + (size_t)blockIdx.z * a.a_batch_stride;
     const T* B = static_cast<const T*>(a.B) + (size_t)g * a.b_group_stride;
 
     const int tid = threadIdx.x;
@@ -118,7 +122,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmArgs a) {
         __syncthreads();
     }
 
-    TC* C = static_cast<TC*>(a.C);
+    TC* C = static_cast<TC*>(a.C) + (size_t)blockIdx.z * a.c_batch_stride;
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
         const int m = row0 + ty * TM + i;
@@ -128,24 +132,21 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmArgs a) {
             const int n = n0 + tx * 4 + j;
             if (n >= a.N) continue;
             float v = acc[i][j];
-            if (DUAL) {
-                const float gate = v;
-                v = gate / (1.0f + expf(-gate)) * acc2[i][j];
-            }
+            if (DUAL) v = glu_apply(v, acc2[i][j], a.glu);
             stf(C + (size_t)m * a.ldc + n, v);
         }
     }
 }
 
 template <typename T, typename TC, bool DUAL>
-static int gemm_simt_launch(const GemmArgs& a, cudaStream_t s) {
-    if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0) return TB_ERR_ARG;
+static int gemm_simt_launch(const GemmArgs& a, cudaStream_t s, int batches = 1) {
+    if (a.M < 0 || a.N <= 0 || a.K <= 0 || a.G <= 0 || batches <= 0 || batches > 65535) return TB_ERR_ARG;
     if (a.M == 0) return 0;
     const bool small = a.M <= 16 * a.G;
     const int bm = small ? 16 : 64;
     // every group may end in a partly filled tile
     const int tiles = a.group_offsets ? (a.M + bm - 1) / bm + a.G : (a.M + bm - 1) / bm;
-    dim3 grid(tiles, (a.N + GB_N - 1) / GB_N);
+    dim3 grid(tiles, (a.N + GB_N - 1) / GB_N, batches);
     if (small)
         TB_LAUNCH((gemm_simt_kernel<T, TC, 16, DUAL>), grid, 256, 0, s, a);
     else
@@ -159,7 +160,8 @@ extern "C" {
     int NAME(const void* A, const int* a_rows, const void* B, void* C, const int* group_offsets,               \
              long long b_group_stride, int lda, int ldb, int ldc, int M, int N, int K, int G, int out_kind,    \
              cudaStream_t s) {                                                                                  \
-        GemmArgs a{A, a_rows, B, C, group_offsets, b_group_stride, lda, ldb, ldc, M, N, K, G};                  \
+        GemmArgs a{A, a_rows, B, C, group_offsets, b_group_stride, lda, ldb, ldc, M, N, K, G, GluRule{0, 0.f, 0.f}, \
+                   0, 0};                                                                                       \
         if (out_kind == 0) return gemm_simt_launch<T, T, false>(a, s);                                          \
         if (out_kind == 1) return gemm_simt_launch<T, float, false>(a, s);                                      \
         if (out_kind == 2) return gemm_simt_launch<T, T, true>(a, s);                                           \
@@ -167,9 +169,38 @@ extern "C" {
     }
 TB_GEMM(tb_gemm_simt_f32, float)
 TB_GEMM(tb_gemm_simt_bf16, __nv_bfloat16)
+
+// The (gate, up) pair product with the clamped form of the gate: g' = min(g, limit), u' = clamp(u, -limit, limit),
+// C = g' * sigmoid(alpha g') * (u' + 1).
+#define TB_GEMM_GLU(NAME, T)                                                                                    \
+    int NAME(const void* A, const int* a_rows, const void* B, void* C, const int* group_offsets,               \
+             long long b_group_stride, int lda, int ldb, int ldc, int M, int N, int K, int G, float alpha,     \
+             float limit, cudaStream_t s) {                                                                     \
+        GemmArgs a{A, a_rows, B, C, group_offsets, b_group_stride, lda, ldb, ldc, M, N, K, G,                   \
+                   GluRule{1, alpha, limit}, 0, 0};                                                             \
+        return gemm_simt_launch<T, T, true>(a, s);                                                              \
+    }
+TB_GEMM_GLU(tb_gemm_simt_glu_f32, float)
+TB_GEMM_GLU(tb_gemm_simt_glu_bf16, __nv_bfloat16)
+
+// `batches` independent products of the same shape: batch b reads A + b * a_stride (rows M, pitch lda), the matrix
+// B + b * b_stride [N, K] and writes C + b * c_stride (the heads of a mixer whose heads have matrices of their own).
+#define TB_GEMM_BATCHED(NAME, T)                                                                                \
+    int NAME(const void* A, const void* B, void* C, long long a_stride, long long b_stride, long long c_stride, \
+             int lda, int ldb, int ldc, int M, int N, int K, int batches, cudaStream_t s) {                     \
+        GemmArgs a{A, nullptr, B, C, nullptr, b_stride, lda, ldb, ldc, M, N, K, 1, GluRule{0, 0.f, 0.f},        \
+                   a_stride, c_stride};                                                                         \
+        return gemm_simt_launch<T, T, false>(a, s, batches);                                                    \
+    }
+TB_GEMM_BATCHED(tb_gemm_simt_batched_f32, float)
+TB_GEMM_BATCHED(tb_gemm_simt_batched_bf16, __nv_bfloat16)
 }
 
 // replayable from C++ (tape.h)
 #include "tape.h"
 TB_TAPE_REGISTER(tb_gemm_simt_f32)
 TB_TAPE_REGISTER(tb_gemm_simt_bf16)
+TB_TAPE_REGISTER(tb_gemm_simt_glu_f32)
+TB_TAPE_REGISTER(tb_gemm_simt_glu_bf16)
+TB_TAPE_REGISTER(tb_gemm_simt_batched_f32)
+TB_TAPE_REGISTER(tb_gemm_simt_batched_bf16)

@@ -48,6 +48,7 @@ struct SkinnyArgs {
     const int* row_group;   // [M] group of every row, rows in any order (instead of group_offsets and x_rows), or null
     int x_div;              // with row_group: row m reads X[m / x_div] and writes Y[m]
     int w_constant;         // W is a weight: nothing the kernel before this one may have written
+    GluRule glu;            // DUAL: how the (gate, up) pair becomes one value
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
                 v += red[w_n][w][0][r][c];
                 if (DUAL) v2 += red[w_n][w][NMAT - 1][r][c];
             }
-            if (DUAL) v = v / (1.0f + expf(-v)) * v2;
+            if (DUAL) v = glu_apply(v, v2, a.glu);
             stf(static_cast<TY*>(a.Y) + (size_t)(listed ? list[chunk + r] : chunk + r) * a.ldy + nb0 + cc, v);
         }
     }
@@ -280,15 +281,15 @@ static int skinny_launch_nt(const SkinnyArgs& a, int out_kind, cudaStream_t s) {
     return TB_ERR_ARG;
 }
 
-extern "C" {
 // out_kind: 0 = bfloat16 out, 1 = float out, 2 = swiglu pair (bfloat16 out).  M is the number of rows
 // over all groups; max_group_rows bounds the rows of any ONE group (for experts: the number of tokens,
 // since a token picks an expert at most once) and only chooses how many rows a pass takes at once.
 // w_constant: W holds weights, which no kernel writes, so a block may read its first weights before it waits for
 // the kernel before it; 0 when W is itself a result (the router of prompts passes the activations as W).
-int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,
+static int skinny_entry(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,
                         long long w_group_stride, int ldx, int ldw, int ldy, int M, int N, int K, int G, int out_kind,
-                        int max_group_rows, const int* row_group, int x_div, int w_constant, cudaStream_t s) {
+                        int max_group_rows, const int* row_group, int x_div, int w_constant, GluRule glu,
+                        cudaStream_t s) {
     if (M < 0 || N <= 0 || K <= 0 || G <= 0) return TB_ERR_ARG;
     if (row_group && (group_offsets || x_rows || x_div < 1)) return TB_ERR_ARG;
     if (row_group && M > SK_WARPS * 32) return TB_ERR_UNSUPPORTED;
@@ -296,7 +297,7 @@ int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y
     if (((uintptr_t)X | (uintptr_t)W) & 15) return TB_ERR_UNSUPPORTED;
     if (M == 0) return 0;
     SkinnyArgs a{(const __nv_bfloat16*)X, x_rows, (const __nv_bfloat16*)W, Y, group_offsets, w_group_stride,
-                 ldx, ldw, ldy, M, N, K, G, row_group, x_div, w_constant};
+                 ldx, ldw, ldy, M, N, K, G, row_group, x_div, w_constant, glu};
     int rows = (max_group_rows > 0 && max_group_rows < M) ? max_group_rows : M;
     if (G > 1) {
         // A pass takes 8, 16 or 32 rows of a group and a thread's registers are sized by the pass (with 16 rows the
@@ -310,8 +311,25 @@ int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y
     if (rows <= 16) return skinny_launch_nt<2>(a, out_kind, s);
     return skinny_launch_nt<4>(a, out_kind, s);
 }
+
+extern "C" {
+int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,
+                        long long w_group_stride, int ldx, int ldw, int ldy, int M, int N, int K, int G, int out_kind,
+                        int max_group_rows, const int* row_group, int x_div, int w_constant, cudaStream_t s) {
+    return skinny_entry(X, x_rows, W, Y, group_offsets, w_group_stride, ldx, ldw, ldy, M, N, K, G, out_kind,
+                        max_group_rows, row_group, x_div, w_constant, GluRule{0, 0.f, 0.f}, s);
+}
+// The (gate, up) pair product with the clamped form of the gate (see GluRule, kind 1).
+int tb_gemm_skinny_glu_bf16(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,
+                            long long w_group_stride, int ldx, int ldw, int ldy, int M, int N, int K, int G,
+                            int max_group_rows, const int* row_group, int x_div, int w_constant, float alpha,
+                            float limit, cudaStream_t s) {
+    return skinny_entry(X, x_rows, W, Y, group_offsets, w_group_stride, ldx, ldw, ldy, M, N, K, G, 2, max_group_rows,
+                        row_group, x_div, w_constant, GluRule{1, alpha, limit}, s);
+}
 }
 
 // replayable from C++ (tape.h)
 #include "tape.h"
 TB_TAPE_REGISTER(tb_gemm_skinny_bf16)
+TB_TAPE_REGISTER(tb_gemm_skinny_glu_bf16)

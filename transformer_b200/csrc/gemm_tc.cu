@@ -73,6 +73,7 @@ struct TcArgs {
     int out_float;
     int tiles_m;        // row tiles (with groups: an upper bound; tiles past the last group are skipped)
     int n_tile;         // rows of B in a tile: a multiple of 16 up to TC_BN (fewer when that fills the SMs better)
+    GluRule glu;        // dual: how the (gate, up) pair becomes one value
 };
 
 // ---- the kernel ----------------------------------------------------------------------------
@@ -294,7 +295,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
                     // per value with only these four warps on the SM to hide them: measured, the epilogue of a tile
                     // took 7 to 18 us, as long as streaming half of the tile's weights.
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __fdividef(v[i] * u[i], 1.0f + __expf(-v[i]));
+                    for (int i = 0; i < 32; ++i) v[i] = glu_apply_fast(v[i], u[i], a.glu);
                 }
                 if (wide) {
                     // A lane holds 32 columns of ONE row: stored from here, every instruction of the warp would touch
@@ -492,13 +493,12 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, cud
     return tb_last_error();
 }
 
-extern "C" {
 // C[m] = A[m] . B[g(m)]^T.  A [M, K] (rows sorted by group), B [G, rows_b, K] with rows_b = N (or 2N when
 // out_kind == 2: gate rows then up rows).  out_kind: 0 bfloat16, 1 float, 2 swiglu (bfloat16).
 // Refuses (TB_ERR_UNSUPPORTED) what TMA cannot address: K or a pitch that is no multiple of 8,
 // a base that is not 16-byte aligned.
-int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offsets, int lda, int ldb, int ldc, int M,
-                    int N, int K, int G, int out_kind, cudaStream_t s) {
+static int gemm_tc_entry(const void* A, const void* B, void* C, const int* group_offsets, int lda, int ldb, int ldc,
+                         int M, int N, int K, int G, int out_kind, GluRule glu, cudaStream_t s) {
     if (M < 0 || N <= 0 || K <= 0 || G <= 0 || out_kind < 0 || out_kind > 2) return TB_ERR_ARG;
     if (K % 8 || lda % 8 || ldb % 8) return TB_ERR_UNSUPPORTED;
     if (((uintptr_t)A | (uintptr_t)B) & 15) return TB_ERR_UNSUPPORTED;
@@ -548,10 +548,21 @@ int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offs
     // and what counts is how few bytes its start needs.  With K = 4,096 both forms measure the same, and with wide
     // experts (K or N of 14,336) the single blocks are 4..20 % faster (1.41 against 1.18 PFLOP/s at 2,048 rows).
     const bool pair = (long long)M >= 1024ll * G && K < 2048;
-    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, 0, n_tile};
+    TcArgs a{C, group_offsets, err_ptr, ldc, M, N, K, G, rows_b, dual, out_kind == 1, 0, n_tile, glu};
     rc = pair ? tc_launch<2>(ma, mb, a, s) : tc_launch<1>(ma, mb, a, s);
     if (pair && rc == TB_ERR_UNSUPPORTED) rc = tc_launch<1>(ma, mb, a, s);
     return rc;
+}
+
+extern "C" {
+int tb_gemm_tc_bf16(const void* A, const void* B, void* C, const int* group_offsets, int lda, int ldb, int ldc, int M,
+                    int N, int K, int G, int out_kind, cudaStream_t s) {
+    return gemm_tc_entry(A, B, C, group_offsets, lda, ldb, ldc, M, N, K, G, out_kind, GluRule{0, 0.f, 0.f}, s);
+}
+// The (gate, up) pair product with the clamped form of the gate (see GluRule, kind 1).
+int tb_gemm_tc_glu_bf16(const void* A, const void* B, void* C, const int* group_offsets, int lda, int ldb, int ldc,
+                        int M, int N, int K, int G, float alpha, float limit, cudaStream_t s) {
+    return gemm_tc_entry(A, B, C, group_offsets, lda, ldb, ldc, M, N, K, G, 2, GluRule{1, alpha, limit}, s);
 }
 
 // Nonzero if any tensor-core product gave up on a wait since the last call (1 producer, 2 MMA,
@@ -583,4 +594,5 @@ int tb_gather_rows_bf16(const void* x, const int* rows, void* out, int M, int d,
 // replayable from C++ (tape.h)
 #include "tape.h"
 TB_TAPE_REGISTER(tb_gemm_tc_bf16)
+TB_TAPE_REGISTER(tb_gemm_tc_glu_bf16)
 TB_TAPE_REGISTER(tb_gather_rows_bf16)

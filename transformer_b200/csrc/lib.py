@@ -43,6 +43,18 @@ _SIGNATURES: Dict[str, str] = {
     "tb_sample": "plpiififpp",
     "tb_kernel_status_async": "p",
     "tb_random_fill_f32": "plulf", "tb_random_fill_bf16": "plulf",
+    "tb_embed_scaled_f32": "pppiif", "tb_embed_scaled_bf16": "pppiif",
+    "tb_post_add_rmsnorm_f32": "pppppipfppfpii", "tb_post_add_rmsnorm_bf16": "pppppipfppfpii",
+    "tb_gemm_simt_glu_f32": "pppppliiiiiiiff", "tb_gemm_simt_glu_bf16": "pppppliiiiiiiff",
+    "tb_gemm_simt_batched_f32": "pppllliiiiiii", "tb_gemm_simt_batched_bf16": "pppllliiiiiii",
+    "tb_gemm_skinny_glu_bf16": "pppppliiiiiiiipiiff",
+    "tb_gemm_tc_glu_bf16": "ppppiiiiiiiff",
+    "tb_router_scored_f32": "pppppppppiiii", "tb_router_scored_bf16": "pppppppppiiii",
+    "tb_moe_identity_rows_f32": "pppppiiii", "tb_moe_identity_rows_bf16": "pppppiiii",
+    "tb_mlstm_scan_f32": "pppppppiiiiiff", "tb_mlstm_scan_bf16": "pppppppiiiiiff",
+    "tb_mlstm_out_f32": "ppippiiif", "tb_mlstm_out_bf16": "ppippiiif",
+    "tb_latent_prep_f32": "pippfpppppippiiiii", "tb_latent_prep_bf16": "pippfpppppippiiiii",
+    "tb_latent_attention_f32": "pppppppppppiiiiiiiiiif", "tb_latent_attention_bf16": "pppppppppppiiiiiiiiiif",
 }
 class TapeArg(ctypes.Union):
     _fields_ = [("p", ctypes.c_void_p), ("i", ctypes.c_int), ("f", ctypes.c_float), ("l", ctypes.c_longlong),
@@ -63,7 +75,7 @@ class TapeMap(ctypes.Structure):
     _fields_ = [("base", ctypes.c_ulonglong), ("size", ctypes.c_ulonglong), ("delta", ctypes.c_longlong)]
 
 
-_NO_STREAM = {"tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
+_NO_STREAM = {"tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
               "tb_attention_tc_tile_tokens": ""}
 
 _lock = threading.Lock()
@@ -309,6 +321,15 @@ def raise_for_status(code: int, recover=None) -> None:
         recover()
     raise KernelError(f"a kernel gave up after its wait limit (code {code}: {_gave_up(int(code))}); the results of "
                       f"the steps since the last check are not valid")
+
+
+def mlstm_state_size(dim: int, vdim: int) -> int:
+    """Floats of state that the matrix-memory kernel keeps per (sequence, head)."""
+    return library().tb_mlstm_state_size(dim, vdim)
+
+
+def latent_attention_tile_tokens(heads: int) -> int:
+    return library().tb_latent_attention_tile_tokens(heads)
 
 
 def attention_prefill_tile_tokens() -> int:

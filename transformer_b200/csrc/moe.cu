@@ -27,14 +27,21 @@ struct DispatchLists {
     unsigned* done;
 };
 
+// How the logits become a choice.  scored == 0: the k largest logits, softmax over the kept (router_pick).
+// scored == 1: softmax over all outputs, the k largest of score + bias, weights = scores (router_pick_scored).
+struct RouterRule {
+    int scored;
+    const float* bias;
+};
+
 template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restrict__ topk_idx,
               float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d, int E, int k,
-              const DispatchLists lists) {
+              const DispatchLists lists, const RouterRule rule) {
     constexpr int EPL = Vec16<T>::N;
     constexpr int UN = 8;
-    extern __shared__ float lg[];   // [E]
+    extern __shared__ float lg[];   // [E] (and [E] more for the scores of the scored rule)
     __shared__ int count[ROUTER_MAX_E + 1];
     __shared__ int cursor[ROUTER_MAX_E];
     __shared__ bool last_block;
@@ -92,7 +99,12 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
     }
     __syncthreads();
     if (warp != 0 && !lists.done) return;
-    if (warp == 0) router_pick(lg, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
+    if (warp == 0) {
+        if (rule.scored)
+            router_pick_scored(lg, lg + E, rule.bias, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
+        else
+            router_pick(lg, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
+    }
     if (!lists.done) return;
     __threadfence();          // this token's choice is visible before the count says so
     __syncthreads();
@@ -297,14 +309,15 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
 
 template <typename T>
 static int router_launch(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out, int nt,
-                         int d, int E, int k, const DispatchLists& lists, cudaStream_t s) {
+                         int d, int E, int k, const DispatchLists& lists, cudaStream_t s,
+                         RouterRule rule = RouterRule{0, nullptr}) {
     if (nt < 0 || d <= 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
     if (E > ROUTER_MAX_E) return TB_ERR_UNSUPPORTED;
     if (nt == 0) return 0;
     int warps = E < ROUTER_WARPS ? E : ROUTER_WARPS;
     if (nt >= 1024 && warps > 4) warps = 4;   // many tokens: fewer, longer-lived warps per token
-    TB_LAUNCH((router_kernel<T>), nt, warps * 32, (size_t)E * sizeof(float), s, 
-        (const T*)x1, (const T*)wr, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
+    TB_LAUNCH((router_kernel<T>), nt, warps * 32, (size_t)E * sizeof(float) * (rule.scored ? 2 : 1), s,
+        (const T*)x1, (const T*)wr, topk_idx, topk_w, logits_out, nt, d, E, k, lists, rule);
     return tb_last_error();
 }
 template <typename T>
@@ -313,6 +326,35 @@ static int combine_launch(const void* y, const int* pair_row, const float* topk_
     if (nt < 0 || d <= 0 || k <= 0) return TB_ERR_ARG;
     if (nt == 0) return 0;
     TB_LAUNCH((moe_combine_kernel<T>), nt, 256, 0, s, (const T*)y, pair_row, topk_w, (T*)delta, d, k);
+    return tb_last_error();
+}
+
+template <typename T>
+__global__ void moe_identity_rows_kernel(const T* __restrict__ x1, T* __restrict__ y,
+                                         const int* __restrict__ group_offsets, const int* __restrict__ sorted_token,
+                                         const int* __restrict__ row_group, int x_div, int d, int first) {
+    pdl_sync();
+    const int m = blockIdx.x;
+    int src;
+    if (row_group) {
+        if (row_group[m] < first) return;
+        src = m / x_div;
+    } else {
+        if (m < group_offsets[first]) return;
+        src = sorted_token[m];
+    }
+    const T* from = x1 + (size_t)src * d;
+    T* to = y + (size_t)m * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) to[c] = from[c];
+}
+template <typename T>
+static int identity_rows_launch(const void* x1, void* y, const int* group_offsets, const int* sorted_token,
+                                const int* row_group, int x_div, int M, int d, int first, cudaStream_t s) {
+    if (M < 0 || d <= 0 || first < 0) return TB_ERR_ARG;
+    if (row_group ? x_div < 1 : !(group_offsets && sorted_token)) return TB_ERR_ARG;
+    if (M == 0) return 0;
+    TB_LAUNCH((moe_identity_rows_kernel<T>), M, 128, 0, s, (const T*)x1, (T*)y, group_offsets, sorted_token, row_group,
+              x_div, d, first);
     return tb_last_error();
 }
 
@@ -330,6 +372,34 @@ int tb_router_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w,
     if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
     return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, logits_out, nt, d, E, k,
                                         DispatchLists{group_offsets, sorted_token, pair_row, done}, s);
+}
+// The scored rule (see RouterRule): softmax over all E outputs, the k largest of score + bias (bias [E] float, or
+// null), weights = the chosen scores.
+int tb_router_scored_f32(const void* x1, const void* wr, const float* bias, int* topk_idx, float* topk_w,
+                         int* group_offsets, int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E,
+                         int k, cudaStream_t s) {
+    if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
+    return router_launch<float>(x1, wr, topk_idx, topk_w, nullptr, nt, d, E, k,
+                                DispatchLists{group_offsets, sorted_token, pair_row, done}, s, RouterRule{1, bias});
+}
+int tb_router_scored_bf16(const void* x1, const void* wr, const float* bias, int* topk_idx, float* topk_w,
+                          int* group_offsets, int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E,
+                          int k, cudaStream_t s) {
+    if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
+    return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, nullptr, nt, d, E, k,
+                                        DispatchLists{group_offsets, sorted_token, pair_row, done}, s,
+                                        RouterRule{1, bias});
+}
+// Experts that hand their input through: the rows of the groups from `first` on receive their token's activations.
+// Sorted rows (group_offsets, sorted_token): rows m >= group_offsets[first], y[m] = x1[sorted_token[m]].
+// Unsorted rows (row_group): rows with row_group[m] >= first, y[m] = x1[m / x_div].
+int tb_moe_identity_rows_f32(const void* x1, void* y, const int* group_offsets, const int* sorted_token,
+                             const int* row_group, int x_div, int M, int d, int first, cudaStream_t s) {
+    return identity_rows_launch<float>(x1, y, group_offsets, sorted_token, row_group, x_div, M, d, first, s);
+}
+int tb_moe_identity_rows_bf16(const void* x1, void* y, const int* group_offsets, const int* sorted_token,
+                              const int* row_group, int x_div, int M, int d, int first, cudaStream_t s) {
+    return identity_rows_launch<__nv_bfloat16>(x1, y, group_offsets, sorted_token, row_group, x_div, M, d, first, s);
 }
 // Router for many tokens (bfloat16, up to 64 experts, a width that is a multiple of 32); `done` as in tb_router_*.
 int tb_router_rows_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out,
@@ -371,6 +441,10 @@ int tb_moe_combine_bf16(const void* y, const int* pair_row, const float* topk_w,
 TB_TAPE_REGISTER(tb_router_f32)
 TB_TAPE_REGISTER(tb_router_bf16)
 TB_TAPE_REGISTER(tb_router_rows_bf16)
+TB_TAPE_REGISTER(tb_router_scored_f32)
+TB_TAPE_REGISTER(tb_router_scored_bf16)
+TB_TAPE_REGISTER(tb_moe_identity_rows_f32)
+TB_TAPE_REGISTER(tb_moe_identity_rows_bf16)
 TB_TAPE_REGISTER(tb_moe_dispatch)
 TB_TAPE_REGISTER(tb_moe_combine_f32)
 TB_TAPE_REGISTER(tb_moe_combine_bf16)

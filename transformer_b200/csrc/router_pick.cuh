@@ -88,3 +88,55 @@ __device__ __forceinline__ void router_pick_serial(float* lg, int* __restrict__ 
     for (int j = 0; j < ROUTER_PICK_SERIAL_K; ++j)
         if (j < k) w_out[j] = p[j] * inv;
 }
+
+// Another rule of choice, by one warp:  s = softmax(lg) over ALL E outputs;  the k largest of s + bias are chosen
+// (ties to the lower index; bias may be null);  the weights are the chosen s as they are, not renormalized.
+// lg is consumed, sc [E] is scratch.
+__device__ __forceinline__ void router_pick_scored(float* lg, float* sc, const float* __restrict__ bias,
+                                                   int* __restrict__ idx_out, float* __restrict__ w_out, int E, int k,
+                                                   int lane) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float p = expf(lg[e] - mx);
+        sc[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) {
+        const float v = sc[e] * inv;
+        sc[e] = v;
+        lg[e] = v + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = lg[e];
+            if (v > best) {
+                best = v;
+                bi = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (bi >= E) bi = 0;
+        if (lane == 0) {
+            idx_out[j] = bi;
+            w_out[j] = sc[bi];
+            lg[bi] = __int_as_float(0x7fc00000);   // NaN compares false with everything: taken
+        }
+        __syncwarp();
+    }
+}

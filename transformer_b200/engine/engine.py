@@ -21,7 +21,7 @@ from ..cache.paged import Cache
 from ..cache.slots import CacheError
 from ..csrc import lib
 from ..parts.block import build_layer, resolve
-from ..parts.base import EMBEDDINGS, HEADS, NORMS
+from ..parts.base import EMBEDDINGS, HEADS, NORMS, NormedDelta
 from ..parts.spec import ModelSpec
 from .context import StepContext, Workspace, weak_callback
 from .tape import LayerTape, moves, run_tensors
@@ -38,6 +38,8 @@ def _pending_signature(pending):
         return None
     if isinstance(pending, torch.Tensor):
         return ("t", pending.data_ptr(), tuple(pending.shape))
+    if isinstance(pending, NormedDelta):      # names a weight of the layer before: equal only for the same layer
+        return ("n", _pending_signature(pending.delta), pending.weight.data_ptr(), pending.eps)
     return ("w", pending.rows.data_ptr(), pending.index.data_ptr(), pending.weights.data_ptr(), pending.k,
             tuple(pending.rows.shape))
 
@@ -365,7 +367,7 @@ class Engine:
             torch.empty((n_out, V), dtype=torch.float32, device=self.device)
         if n_out:
             xn = ctx.scratch("final.xn", (n_out, d), self.dtype)
-            pending = resolve(pending, self.final_norm, ctx.scratch("block.delta", (nt, d), self.dtype))
+            pending = resolve(pending, self.final_norm, ctx.scratch("block.delta", (nt, d), self.dtype), x=x, ctx=ctx)
             self.final_norm.forward(ctx, x, pending, ctx.want_rows, xn)
             self.head_part.forward(ctx, xn, logits)
         return logits

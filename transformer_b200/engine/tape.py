@@ -80,10 +80,11 @@ def run_tensors(layer, cache_view, state) -> Optional[List[torch.Tensor]]:
         for wname in sorted(part.weights):
             out.append(part.weights[wname])
     if cache_view is not None:
-        k, v = getattr(cache_view, "k", None), getattr(cache_view, "v", None)
-        if not (isinstance(k, torch.Tensor) and isinstance(v, torch.Tensor) and type(cache_view).__name__ == "CacheView"):
+        listed = getattr(cache_view, "tensors", None)      # the package's views list their tensors
+        held = listed() if callable(listed) else None
+        if not held or not all(isinstance(t, torch.Tensor) for t in held):
             return None
-        out += [k, v]
+        out += list(held)
     if state is not None:
         out.append(state)
     return out

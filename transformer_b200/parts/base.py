@@ -81,6 +81,17 @@ class WeightedRows:
     k: int
 
 
+@dataclass
+class NormedDelta:
+    """A part's output that still has to be normed before it joins the stream:  x += delta / rms(delta) * weight
+    (a block that norms its parts' outputs as well as their inputs).  ``delta`` is a tensor [nt, d] or a
+    :class:`WeightedRows`.  A norm that sets ``takes_normed_delta`` does that norm, the sum and its own norm in one
+    kernel; for any other norm the block applies it to the stream first (:func:`parts.block.resolve`)."""
+    delta: Any
+    weight: torch.Tensor      # float [d]
+    eps: float
+
+
 class Part:
     graph_safe = False      # see the head of this file; the parts of this package set it
     launches_only = False   # all device work goes through csrc.lib launchers (or reports itself with lib.foreign):
@@ -125,6 +136,7 @@ class NormTail:
 
 class Norm(Part):
     takes_weighted_rows = False
+    takes_normed_delta = False
     can_warm = False           # forward takes ``warm=``: a weight of the next part to fetch into L2 meanwhile
     tails: tuple = ()          # kinds of NormTail that forward(..., tail=) computes along the way
 

@@ -17,7 +17,7 @@ return value is what this block leaves.  A block that wants its sums done at onc
 """
 from __future__ import annotations
 
-from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, WeightedRows
+from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, NormedDelta, WeightedRows
 
 
 def build_layer(spec, dtype, device):
@@ -56,7 +56,7 @@ class Layer:
         nt, d = x.shape
         x1 = ctx.scratch("block.x1", (nt, d), ctx.dtype)
         delta = ctx.scratch("block.delta", (nt, d), ctx.dtype)
-        pending = resolve(pending, self.mixer_norm, delta)
+        pending = resolve(pending, self.mixer_norm, delta, x=x, ctx=ctx)
         self._norm(self.mixer_norm, self.mixer, ctx, x, pending, x1)
         self.mixer.forward(ctx, x1, delta, cache_view, state)
         tail = self.feed_forward.norm_tail(ctx, nt)
@@ -80,9 +80,80 @@ class Layer:
             norm.forward(ctx, x, delta, None, y)
 
 
+@ARRANGEMENTS.register("sandwich")
+class SandwichLayer:
+    """A block that norms what its parts produce as well as what they read:
+
+        x += norm_mb(mixer(norm_m(x)));   x += norm_fb(feed_forward(norm_f(x)))
+
+    ``LayerSpec.extra`` names the two further norms, "mixer_post_norm" and "feed_forward_post_norm"; a layer may
+    have no feed-forward (then it needs neither "feed_forward_post_norm" nor a feed-forward norm).  The mixer's
+    output is handed to the feed-forward's norm as a :class:`NormedDelta`, so its norm, the sum into the stream and
+    the next norm are one kernel; the feed-forward's output (the experts' weighted rows, unsummed) is normed and
+    added by the block's last kernel.  The block takes any pending contribution and leaves none."""
+
+    def __init__(self, spec, dtype, device):
+        extra = dict(spec.extra)
+        if spec.mixer_norm is None or "mixer_post_norm" not in extra:
+            raise ValueError("the sandwich arrangement needs a norm before the mixer and a 'mixer_post_norm'")
+        self.spec = spec
+        self.mixer_norm = NORMS.build(spec.mixer_norm, dtype, device)
+        self.mixer = MIXERS.build(spec.mixer, dtype, device)
+        self.mixer_post_norm = NORMS.build(extra["mixer_post_norm"], dtype, device)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if spec.feed_forward is not None:
+            if spec.feed_forward_norm is None or "feed_forward_post_norm" not in extra:
+                raise ValueError("a sandwich block with a feed-forward needs its norm and a 'feed_forward_post_norm'")
+            self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, dtype, device)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, dtype, device)
+            self.feed_forward_post_norm = NORMS.build(extra["feed_forward_post_norm"], dtype, device)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in self.parts().values())
+
+    @property
+    def launches_only(self) -> bool:
+        return all(p.launches_only for p in self.parts().values())
+
+    def parts(self):
+        out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_post_norm": self.mixer_post_norm}
+        if self.feed_forward is not None:
+            out.update({"feed_forward_norm": self.feed_forward_norm, "feed_forward": self.feed_forward,
+                        "feed_forward_post_norm": self.feed_forward_post_norm})
+        return out
+
+    @staticmethod
+    def _normed(out, post) -> NormedDelta:
+        return NormedDelta(out, post.weights["weight"], post.eps)
+
+    def forward(self, ctx, x, pending, cache_view, state):
+        from .norm import post_add_rmsnorm
+        nt, d = x.shape
+        x1 = ctx.scratch("block.x1", (nt, d), ctx.dtype)
+        delta = ctx.scratch("block.delta", (nt, d), ctx.dtype)
+        pending = resolve(pending, self.mixer_norm, delta, x=x, ctx=ctx)
+        Layer._norm(self.mixer_norm, self.mixer, ctx, x, pending, x1)
+        self.mixer.forward(ctx, x1, delta, cache_view, state)
+        pending = self._normed(delta, self.mixer_post_norm)
+        if self.feed_forward is not None:
+            pending = resolve(pending, self.feed_forward_norm, delta, x=x, ctx=ctx)
+            self.feed_forward_norm.forward(ctx, x, pending, None, x1)
+            lazy = self.feed_forward.forward(ctx, x1, delta)
+            pending = self._normed(delta if lazy is None else lazy, self.feed_forward_post_norm)
+        # the last norm's weight belongs to THIS layer: the sum is done here, so that the layer's launches name no
+        # tensor of another layer (layers of equal parts are replayed with their own tensors put in)
+        post_add_rmsnorm(ctx.dtype, x, pending, None, None, 0.0, None)
+        return None
+
+
 def add_pending(ctx, x, pending) -> None:
     """x += pending, at once and in float, for an arrangement that does not leave the sum to a norm."""
     if pending is None:
+        return
+    if isinstance(pending, NormedDelta):
+        from .norm import post_add_rmsnorm
+        post_add_rmsnorm(ctx.dtype, x, pending, None, None, 0.0, None)
         return
     if isinstance(pending, WeightedRows):
         from .feed_forward import sum_weighted_rows
@@ -92,8 +163,16 @@ def add_pending(ctx, x, pending) -> None:
     x.add_(pending.float())
 
 
-def resolve(pending, norm, into):
-    """A pending WeightedRows stays as it is for a norm that sums it itself; else it is summed into ``into``."""
+def resolve(pending, norm, into, x=None, ctx=None):
+    """A pending WeightedRows stays as it is for a norm that sums it itself; else it is summed into ``into``.  A
+    pending NormedDelta stays for a norm that takes one; else it is normed and added to the stream ``x`` now."""
+    if isinstance(pending, NormedDelta):
+        if getattr(norm, "takes_normed_delta", False):
+            return pending
+        if x is None or ctx is None:
+            raise ValueError("a normed delta can only be resolved with the stream at hand")
+        add_pending(ctx, x, pending)
+        return None
     if isinstance(pending, WeightedRows) and not norm.takes_weighted_rows:
         from .feed_forward import sum_weighted_rows
         sum_weighted_rows(pending, into)

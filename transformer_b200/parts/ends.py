@@ -15,17 +15,22 @@ from .linear import matmul_nt
 
 @EMBEDDINGS.register("lookup")
 class Lookup(Embedding):
-    """params: vocab, width.  x[i] = table[tok_i] as float, no scaling."""
+    """params: vocab, width, scale (default 1).  x[i] = table[tok_i] * scale, in float."""
     graph_safe = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
         self.vocab, self.width = int(params["vocab"]), int(params["width"])
+        self.scale = float(params.get("scale", 1.0))
 
     def parameters(self):
         return {"table": ParamDecl((self.vocab, self.width))}
 
     def forward(self, ctx, x) -> None:
+        if self.scale != 1.0:
+            lib.call("tb_embed_scaled_" + lib.suffix(self.dtype), lib.ptr(ctx.tok_ids), lib.ptr(self.weights["table"]),
+                     lib.ptr(x), x.shape[0], self.width, self.scale)
+            return
         lib.call("tb_embed_" + lib.suffix(self.dtype), lib.ptr(ctx.tok_ids), lib.ptr(self.weights["table"]),
                  lib.ptr(x), x.shape[0], self.width)
 

@@ -42,11 +42,20 @@ class DenseSwiGLU(FeedForward):
 
 @FEED_FORWARDS.register("moe")
 class MoE(FeedForward):
-    """params: width, di, nexp, nexp_use.
+    """params: width, di, nexp, nexp_use; optional: scoring, correction, identity, glu_alpha, glu_limit.
 
     router logits (float) -> the nexp_use largest, equal logits to the lower expert -> softmax over
     the kept logits (compute.rs:375-394) -> expert SwiGLU (compute.rs:320-328) -> weighted sum in
-    descending-logit order, in float (compute.rs:329-330)."""
+    descending-logit order, in float (compute.rs:329-330).
+
+    Other routers and experts, by parameter:
+    * ``scoring`` = "all": scores = softmax over ALL router outputs; the nexp_use largest of score + correction
+      are chosen (``correction`` = True: a learned float vector, one entry per router output; equal values to the
+      lower index); the weights are the chosen scores as they are.
+    * ``identity`` = n: the router has nexp + n outputs, and the last n stand for experts without weights whose
+      output is their input.
+    * ``glu_limit`` (with ``glu_alpha``): the expert's pair becomes g' * sigmoid(alpha g') * (u' + 1) with
+      g' = min(g, limit), u' = clamp(u, -limit, limit), instead of silu(g) * u."""
     graph_safe = True
     launches_only = True
 
@@ -56,17 +65,31 @@ class MoE(FeedForward):
         self.di = int(params["di"])
         self.E = int(params["nexp"])
         self.k = int(params["nexp_use"])
-        if not (0 < self.k <= self.E):
-            raise ValueError(f"experts per token {self.k} must lie in 1..{self.E}")
-        if self.E > 1024:
-            raise ValueError(f"the routing kernels take up to 1024 experts, got {self.E}")
+        if not (0 < self.k <= self.E + int(params.get("identity", 0))):
+            raise ValueError(f"experts per token {self.k} must lie in 1..{self.E + int(params.get('identity', 0))}")
+        self.identity = int(params.get("identity", 0))
+        self.R = self.E + self.identity           # router outputs
+        if self.R > 1024:
+            raise ValueError(f"the routing kernels take up to 1024 experts, got {self.R}")
+        self.scoring = params.get("scoring", "kept")
+        if self.scoring not in ("kept", "all"):
+            raise ValueError(f"unknown router scoring {self.scoring!r}")
+        self.correction = bool(params.get("correction", False))
+        if self.correction and self.scoring != "all":
+            raise ValueError("a correction of the choice goes with scoring 'all'")
+        limit = params.get("glu_limit")
+        self.glu = None if limit is None else (float(params.get("glu_alpha", 1.0)), float(limit))
+        self.plain_router = self.scoring == "kept" and not self.identity
 
     def parameters(self):
-        return {
-            "router": ParamDecl((self.E, self.d)),
+        decl = {
+            "router": ParamDecl((self.R, self.d)),
             "wgu": ParamDecl((self.E, 2 * self.di, self.d)),
             "wd": ParamDecl((self.E, self.d, self.di)),
         }
+        if self.correction:
+            decl["correction"] = ParamDecl((self.R,), "norm", "normal")
+        return decl
 
     def early_weights(self):
         """The router's matrix: small, and every token's block waits for all of it."""
@@ -79,14 +102,22 @@ class MoE(FeedForward):
         nt = x1.shape[0]
         idx = ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32)
         w = ctx.scratch("moe.topk_w", (nt, self.k), torch.float32)
-        if self.dtype == torch.bfloat16 and nt > ROUTER_ROWS_FROM and self.E <= 64:
+        if self.scoring == "all":
+            # scores over all outputs, choice with the correction, the block that finishes last builds the lists
+            done = ctx.scratch("moe.done", (1,), torch.int32, zero=True) if lists is not None else None
+            offsets, sorted_token, pair_row = lists if lists is not None else (None, None, None)
+            lib.call("tb_router_scored_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
+                     lib.ptr(self.weights.get("correction")), lib.ptr(idx), lib.ptr(w), lib.ptr(offsets),
+                     lib.ptr(sorted_token), lib.ptr(pair_row), lib.ptr(done), nt, self.d, self.R, self.k)
+            return idx, w, lists is not None
+        if self.dtype == torch.bfloat16 and nt > ROUTER_ROWS_FROM and self.R <= 64:
             # many tokens, few experts: 16 tokens' logits are a tensor-core tile, the activations are read once, and
             # the block that finishes last builds the dispatch lists
             done = ctx.scratch("moe.done", (1,), torch.int32, zero=True) if lists is not None else None
             offsets, sorted_token, pair_row = lists if lists is not None else (None, None, None)
             if lib.try_call("tb_router_rows_bf16", lib.ptr(x1), lib.ptr(self.weights["router"]), lib.ptr(idx), lib.ptr(w),
                             lib.ptr(logits_out), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
-                            lib.ptr(done), nt, self.d, self.E, self.k):
+                            lib.ptr(done), nt, self.d, self.R, self.k):
                 return idx, w, lists is not None
         # a few tokens: the block that finishes last builds the lists, which saves a kernel on the way to the experts
         fused = lists is not None and nt <= ROUTER_ROWS_FROM
@@ -94,12 +125,12 @@ class MoE(FeedForward):
         offsets, sorted_token, pair_row = lists if fused else (None, None, None)
         lib.call("tb_router_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
                  lib.ptr(idx), lib.ptr(w), lib.ptr(logits_out), lib.ptr(offsets), lib.ptr(sorted_token),
-                 lib.ptr(pair_row), lib.ptr(done), nt, self.d, self.E, self.k)
+                 lib.ptr(pair_row), lib.ptr(done), nt, self.d, self.R, self.k)
         return idx, w, fused
 
     def norm_tail(self, ctx, nt):
-        """For a few tokens the router rides along with the norm before this part."""
-        if nt > ROUTER_TAIL_ROWS:
+        """For a few tokens the router rides along with the norm before this part (the plain rule of choice)."""
+        if nt > ROUTER_TAIL_ROWS or self.scoring != "kept":
             return None
         return NormTail("router", weights=self.weights["router"], k=self.k,
                         index=ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32),
@@ -117,11 +148,14 @@ class MoE(FeedForward):
             y = ctx.scratch("moe.y", (M, self.d), self.dtype)
             pairs = idx.view(-1)
             if gemm_skinny(x1, self.weights["wgu"], h, groups=self.E, out_kind=2, max_group_rows=nt, row_group=pairs,
-                           x_div=self.k) and \
+                           x_div=self.k, glu=self.glu) and \
                     gemm_skinny(h, self.weights["wd"], y, groups=self.E, max_group_rows=nt, row_group=pairs):
                 ctx.record("moe.topk_idx", idx)
+                if self.identity:       # pairs that chose an expert without weights: the token's own row
+                    lib.call("tb_moe_identity_rows_" + sfx, lib.ptr(x1), lib.ptr(y), 0, 0, lib.ptr(pairs), self.k, M,
+                             self.d, self.E)
                 return WeightedRows(y, _identity_rows(M, x1.device), w, self.k)
-        offsets = ctx.scratch("moe.offsets", (self.E + 1,), torch.int32)
+        offsets = ctx.scratch("moe.offsets", (self.R + 1,), torch.int32)
         sorted_token = ctx.scratch("moe.sorted_token", (M,), torch.int32)
         pair_row = ctx.scratch("moe.pair_row", (M,), torch.int32)
         if tail is not None:
@@ -131,12 +165,15 @@ class MoE(FeedForward):
         ctx.record("moe.topk_idx", idx)
         if not listed:
             lib.call("tb_moe_dispatch", lib.ptr(idx), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
-                     M, self.k, self.E)
+                     M, self.k, self.R)
         h = ctx.scratch("moe.h", (M, self.di), self.dtype)
         grouped_matmul(x1, self.weights["wgu"], h, a_rows=sorted_token, group_offsets=offsets, groups=self.E,
-                       swiglu=True, max_group_rows=nt, scratch=ctx.scratch)
+                       swiglu=True, max_group_rows=nt, scratch=ctx.scratch, glu=self.glu)
         y = ctx.scratch("moe.y", (M, self.d), self.dtype)
         grouped_matmul(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E, max_group_rows=nt)
+        if self.identity:               # the rows after the last real expert's: their tokens' own rows
+            lib.call("tb_moe_identity_rows_" + sfx, lib.ptr(x1), lib.ptr(y), lib.ptr(offsets), lib.ptr(sorted_token),
+                     0, 1, M, self.d, self.E)
         # the weighted sum over the chosen experts is left to the norm that follows (fused there)
         return WeightedRows(y, pair_row, w, self.k)
 

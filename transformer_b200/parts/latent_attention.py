@@ -1,0 +1,108 @@
+"""Attention through a low-rank latent, with a sliding window and a rotated key part that all heads share.
+
+    zq = Wdq x1,  cq = zq / rms(zq) * wq_norm,  q = Wuq cq                   per head: [dim plain | rot_dim rotated]
+    [zc | zr] = Wdkv x1,  c = zc / rms(zc) * wc_norm,  kr = rotate(zr)      one row per token, cached: [c | kr]
+    head h:  k_plain = Wuk_h c,  v = Wuv_h c
+    score_h(t, j) = (q_plain . k_plain_j + rotate(q_rot) . kr_j) * scale,   j visible iff 0 <= t - j < window
+    out = Wo concat_h(softmax(score_h) v_h)
+
+Nothing per head is cached or formed for cached tokens: the query goes to the latent's side
+(Wuk_h^T q_plain, a product batched over the heads), the attention kernel runs over the shared rows
+[c | kr] with c as the value as well, and Wuv_h is applied to the attention's result (csrc/latent.cu).
+A layer with ``own_latent`` False makes no latent: it reads the cache of the run named by its
+``RunEntry.cache_of``, with its own Wuk, Wuv, queries and window.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import lib
+from .base import MIXERS, POSITIONS, CacheNeed, Mixer, ParamDecl
+from .linear import batched_matmul, matmul_nt
+from .spec import PartSpec
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Mixer):
+    """params: width, heads, dim, rot_dim, vdim, kv_rank, q_rank, window, scale, eps, own_latent, position (a
+    PartSpec of a rotary encoding of the first ``dh`` entries of the rotated part, pairing "half")."""
+    launches_only = True
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        g = lambda n: int(params[n])
+        self.d, self.H, self.dim, self.rot, self.vdim = g("width"), g("heads"), g("dim"), g("rot_dim"), g("vdim")
+        self.rank, self.q_rank, self.window = g("kv_rank"), g("q_rank"), g("window")
+        self.scale, self.eps = float(params["scale"]), float(params["eps"])
+        self.own_latent = bool(params.get("own_latent", True))
+        pos = params.get("position")
+        if not isinstance(pos, PartSpec):
+            raise ValueError("latent attention needs the rotary encoding of its rotated part ('position')")
+        self.position = POSITIONS.build(pos, dtype, device)
+        self.rdims = int(pos.get()["dh"])
+        if self.rdims > self.rot or self.rdims % 2 or pos.get().get("pairing") != "half":
+            raise ValueError(f"the rotated part of {self.rot} entries takes a rotation of an even number of them, "
+                             f"halves paired; got {self.rdims}, {pos.get().get('pairing')!r}")
+        if self.window <= 0:
+            raise ValueError(f"the window must hold at least the token itself, got {self.window}")
+        if self.rank > 512:
+            raise ValueError(f"the latent attention kernel takes latents of up to 512 entries, got {self.rank}")
+        self.q_head = self.dim + self.rot
+        self.tile = lib.latent_attention_tile_tokens(self.H)
+        self.tile_sizes = [self.tile]
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.position.graph_safe
+
+    def parameters(self):
+        down = self.q_rank + (self.rank + self.rot if self.own_latent else 0)
+        decl = {
+            "wdown": ParamDecl((down, self.d)),            # rows: Wdq, then (own latent) Wdkv
+            "q_norm": ParamDecl((self.q_rank,), "norm", "ones"),
+            "uq": ParamDecl((self.H * self.q_head, self.q_rank)),
+            "uk": ParamDecl((self.H * self.dim, self.rank)),
+            "uv": ParamDecl((self.H * self.vdim, self.rank)),
+            "wo": ParamDecl((self.d, self.H * self.vdim)),
+        }
+        if self.own_latent:
+            decl["c_norm"] = ParamDecl((self.rank,), "norm", "ones")
+        return decl
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        # the product that takes the queries to the latent's side wants Wuk_h^T as its [out, in] matrix
+        uk = self.weights.pop("uk")
+        self.weights["ukT"] = uk.view(self.H, self.dim, self.rank).transpose(1, 2).contiguous()
+
+    def cache_need(self):
+        return CacheNeed("latent", 1, self.rank + self.rot, (("rank", self.rank), ("rot", self.rot)))
+
+    def forward(self, ctx, x1, out, cache, state) -> None:
+        nt, H = x1.shape[0], self.H
+        sfx = lib.suffix(self.dtype)
+        w = self.weights
+        wa = w["wdown"].shape[0]
+        a = ctx.scratch("latent.a", (nt, wa), self.dtype)
+        matmul_nt(x1, w["wdown"], a)
+        cq = ctx.scratch("latent.cq", (nt, self.q_rank), self.dtype)
+        table = ctx.page_table(cache)
+        cos, sin, _ = self.position.rotation()
+        write = self.own_latent and cache.writable
+        lib.call("tb_latent_prep_" + sfx, lib.ptr(a), wa, lib.ptr(w["q_norm"]), lib.ptr(w.get("c_norm")), self.eps,
+                 lib.ptr(cq), lib.ptr(cache.kv) if write else 0, lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos),
+                 lib.ptr(table), ctx.max_pages, lib.ptr(cos), lib.ptr(sin), nt, self.q_rank, self.rank, self.rot,
+                 self.rdims)
+        q = ctx.scratch("latent.q", (nt, H * self.q_head), self.dtype)
+        matmul_nt(cq, w["uq"], q)
+        qa = ctx.scratch("latent.qa", (nt, H, self.rank), self.dtype)
+        batched_matmul(q.view(nt, H, self.q_head)[:, :, :self.dim], w["ukT"], qa)
+        ol = ctx.scratch("latent.ol", (nt, H, self.rank), self.dtype)
+        tiles = ctx.tiles(self.tile)
+        lib.call("tb_latent_attention_" + sfx, lib.ptr(qa), lib.ptr(q), lib.ptr(ol), lib.ptr(cache.kv),
+                 lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos), lib.ptr(table),
+                 lib.ptr(cos), lib.ptr(sin), tiles.count, ctx.max_pages, H * self.q_head, self.q_head, self.dim, H,
+                 self.rank, self.rot, self.rdims, self.window, self.scale)
+        o = ctx.scratch("latent.o", (nt, H, self.vdim), self.dtype)
+        batched_matmul(ol, w["uv"].view(H, self.vdim, self.rank), o)
+        matmul_nt(o.view(nt, H * self.vdim), w["wo"], out)

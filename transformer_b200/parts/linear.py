@@ -16,8 +16,9 @@ import torch
 from ..csrc import lib
 
 
-def gemm_simt(a, w, out, *, a_rows=None, group_offsets=None, groups=1, rows=None, out_kind=0) -> None:
-    """out[m] = a[a_rows[m] or m] . w[g(m)]^T ; w is [N, K] or [G, N(or 2N), K]."""
+def gemm_simt(a, w, out, *, a_rows=None, group_offsets=None, groups=1, rows=None, out_kind=0, glu=None) -> None:
+    """out[m] = a[a_rows[m] or m] . w[g(m)]^T ; w is [N, K] or [G, N(or 2N), K].  ``glu`` = (alpha, limit): the
+    clamped form of the (gate, up) pair instead of swiglu (with out_kind 2)."""
     M = out.shape[0] if rows is None else rows
     K = a.shape[-1]
     N = out.shape[-1]
@@ -28,8 +29,34 @@ def gemm_simt(a, w, out, *, a_rows=None, group_offsets=None, groups=1, rows=None
         stride = 0
         ldb = w.stride(0)
     assert a.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+    if glu is not None and out_kind == 2:
+        lib.call("tb_gemm_simt_glu_" + lib.suffix(a.dtype), lib.ptr(a), lib.ptr(a_rows), lib.ptr(w), lib.ptr(out),
+                 lib.ptr(group_offsets), stride, a.stride(0), ldb, out.stride(0), M, N, K, groups, float(glu[0]),
+                 float(glu[1]))
+        return
     lib.call("tb_gemm_simt_" + lib.suffix(a.dtype), lib.ptr(a), lib.ptr(a_rows), lib.ptr(w), lib.ptr(out),
              lib.ptr(group_offsets), stride, a.stride(0), ldb, out.stride(0), M, N, K, groups, out_kind)
+
+
+BATCHED_LIBRARY_ROWS = 64   # bfloat16 batched products with at least this many rows go to the library
+
+
+def batched_matmul(a, w, out) -> None:
+    """out[:, b, :] = a[:, b, :] @ w[b].T for every batch b (the heads of a mixer whose heads have matrices of their
+    own).  a [M, batches, K] and out [M, batches, N] may be views with a pitch (the last axis contiguous, the batch
+    axis a fixed stride); w [batches, N, K] contiguous.  float32: the CUDA-core kernel, always.  bfloat16 with many
+    rows: the library's batched product, as dense products go to the library."""
+    M, batches, K = a.shape
+    N = out.shape[-1]
+    assert a.stride(-1) == 1 and out.stride(-1) == 1 and w.is_contiguous() and tuple(w.shape) == (batches, N, K)
+    if M == 0:
+        return
+    if a.dtype == torch.bfloat16 and M >= BATCHED_LIBRARY_ROWS:
+        lib.foreign("bmm", a, w, out)
+        torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+        return
+    lib.call("tb_gemm_simt_batched_" + lib.suffix(a.dtype), lib.ptr(a), lib.ptr(w), lib.ptr(out), a.stride(1),
+             w.stride(0), out.stride(1), a.stride(0), w.stride(1), out.stride(0), M, N, K, batches)
 
 
 DENSE_TC = False           # dense bfloat16 products of many rows: this package's tcgen05 kernel instead of cuBLAS
@@ -39,7 +66,7 @@ SKINNY_MAX_PAIRS = 64      # grouped: up to this many rows over all groups (meas
 
 
 def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kind=0, max_group_rows=0,
-                row_group=None, x_div=1, w_is_weight=True) -> bool:
+                row_group=None, x_div=1, w_is_weight=True, glu=None) -> bool:
     """The decode kernel (bfloat16, tensor cores, weights streamed once).  False if it refuses the sizes.
     With ``row_group`` ([M] int32) the rows are unsorted: row m belongs to group row_group[m], reads
     a[m // x_div] and writes out[m] (no offsets, no gathered rows).  ``w_is_weight=False``: ``w`` was computed by
@@ -50,17 +77,25 @@ def gemm_skinny(a, w, out, *, a_rows=None, group_offsets=None, groups=1, out_kin
     else:
         stride, ldw = 0, w.stride(0)
     assert a.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1
+    if glu is not None and out_kind == 2:
+        return lib.try_call("tb_gemm_skinny_glu_bf16", lib.ptr(a), lib.ptr(a_rows), lib.ptr(w), lib.ptr(out),
+                            lib.ptr(group_offsets), stride, a.stride(0), ldw, out.stride(0), M, N, K, groups,
+                            max_group_rows, lib.ptr(row_group), x_div, 1 if w_is_weight else 0, float(glu[0]),
+                            float(glu[1]))
     return lib.try_call("tb_gemm_skinny_bf16", lib.ptr(a), lib.ptr(a_rows), lib.ptr(w), lib.ptr(out),
                         lib.ptr(group_offsets), stride, a.stride(0), ldw, out.stride(0), M, N, K, groups, out_kind,
                         max_group_rows, lib.ptr(row_group), x_div, 1 if w_is_weight else 0)
 
 
-def gemm_tc(a, w, out, *, group_offsets=None, groups=1, out_kind=0) -> bool:
+def gemm_tc(a, w, out, *, group_offsets=None, groups=1, out_kind=0, glu=None) -> bool:
     """The prompt kernel (bfloat16, tcgen05 + TMA + TMEM).  Rows of ``a`` are already sorted by group.
     False if it refuses the sizes."""
     M, K, N = out.shape[0], a.shape[-1], out.shape[-1]
     ldw = w.stride(1) if w.dim() == 3 else w.stride(0)
     assert a.stride(-1) == 1 and w.stride(-1) == 1 and out.stride(-1) == 1 and w.is_contiguous()
+    if glu is not None and out_kind == 2:
+        return lib.try_call("tb_gemm_tc_glu_bf16", lib.ptr(a), lib.ptr(w), lib.ptr(out), lib.ptr(group_offsets),
+                            a.stride(0), ldw, out.stride(0), M, N, K, groups, float(glu[0]), float(glu[1]))
     return lib.try_call("tb_gemm_tc_bf16", lib.ptr(a), lib.ptr(w), lib.ptr(out), lib.ptr(group_offsets),
                         a.stride(0), ldw, out.stride(0), M, N, K, groups, out_kind)
 
@@ -88,14 +123,14 @@ def matmul_nt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w_is_weigh
 
 
 def grouped_matmul(a, w, out, *, a_rows=None, group_offsets=None, groups=1, swiglu=False, max_group_rows=0,
-                   scratch=None, w_is_weight: bool = True) -> None:
+                   scratch=None, w_is_weight: bool = True, glu=None) -> None:
     """out[m] = a[a_rows[m] or m] . w[g(m)]^T over rows sorted by group; with swiglu, w[g] holds gate rows
-    then up rows and out = silu(gate) * up.  max_group_rows: a bound on the rows of one group, if known;
+    then up rows and out = silu(gate) * up (or, with ``glu`` = (alpha, limit), the clamped form of the pair).  max_group_rows: a bound on the rows of one group, if known;
     scratch(name, shape, dtype): where the prompt kernel may put the gathered rows."""
     kind = 2 if swiglu else 0
     if a.dtype == torch.bfloat16 and out.shape[0] <= SKINNY_MAX_PAIRS and \
             gemm_skinny(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind,
-                        max_group_rows=max_group_rows, w_is_weight=w_is_weight):
+                        max_group_rows=max_group_rows, w_is_weight=w_is_weight, glu=glu):
         return
     if a.dtype == torch.bfloat16 and w.is_contiguous():
         src = a
@@ -107,6 +142,6 @@ def grouped_matmul(a, w, out, *, a_rows=None, group_offsets=None, groups=1, swig
                 if lib.try_call("tb_gather_rows_bf16", lib.ptr(a), lib.ptr(a_rows), lib.ptr(buf), out.shape[0],
                                 a.shape[-1]):
                     src = buf
-        if src is not None and gemm_tc(src, w, out, group_offsets=group_offsets, groups=groups, out_kind=kind):
+        if src is not None and gemm_tc(src, w, out, group_offsets=group_offsets, groups=groups, out_kind=kind, glu=glu):
             return
-    gemm_simt(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind)
+    gemm_simt(a, w, out, a_rows=a_rows, group_offsets=group_offsets, groups=groups, out_kind=kind, glu=glu)

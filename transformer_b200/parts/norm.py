@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from ..csrc import lib
-from .base import NORMS, Norm, ParamDecl, WeightedRows
+from .base import NORMS, Norm, NormedDelta, ParamDecl, WeightedRows
 
 
 @NORMS.register("rmsnorm")
@@ -12,6 +12,7 @@ class RMSNorm(Norm):
     graph_safe = True
     launches_only = True
     takes_weighted_rows = True
+    takes_normed_delta = True
     can_warm = True
     tails = ("router",)
 
@@ -24,6 +25,11 @@ class RMSNorm(Norm):
         return {"weight": ParamDecl((self.width,), "norm", "ones")}
 
     def forward(self, ctx, x, delta, rows, y, warm=None, tail=None) -> None:
+        if isinstance(delta, NormedDelta):
+            if tail is not None:
+                raise ValueError("a norm that is handed a normed delta computes no tail")
+            post_add_rmsnorm(self.dtype, x, delta, rows, self.weights["weight"], self.eps, y)
+            return
         n_out = y.shape[0]
         wy = idx = wts = None
         k = 0
@@ -48,3 +54,15 @@ class RMSNorm(Norm):
         lib.call("tb_add_rmsnorm_" + lib.suffix(self.dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
                  lib.ptr(wts), k, lib.ptr(rows), lib.ptr(self.weights["weight"]), self.eps, lib.ptr(y), n_out,
                  self.width, lib.ptr(warm), 0 if warm is None else warm.numel() * warm.element_size())
+
+
+def post_add_rmsnorm(dtype, x, pending: NormedDelta, rows, weight, eps, y) -> None:
+    """x[rows] += pending.delta / rms(pending.delta) * pending.weight (written back when ``rows`` is None), then
+    y = x / rms(x) * weight; with ``y`` None only the sum."""
+    delta, wy, idx, wts, k = pending.delta, None, None, None, 0
+    if isinstance(delta, WeightedRows):
+        wy, idx, wts, k, delta = delta.rows, delta.index, delta.weights, delta.k, None
+    n_out = x.shape[0] if y is None else y.shape[0]
+    lib.call("tb_post_add_rmsnorm_" + lib.suffix(dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
+             lib.ptr(wts), k, lib.ptr(pending.weight), float(pending.eps), lib.ptr(rows), lib.ptr(weight), float(eps),
+             lib.ptr(y), n_out, x.shape[1])

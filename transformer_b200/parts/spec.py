@@ -34,7 +34,7 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]               # None: a layer without one, for arrangements that allow it
     mixer_norm: Optional[PartSpec] = None          # an arrangement says which of these it needs
     feed_forward_norm: Optional[PartSpec] = None
     arrangement: str = "pre_norm"   # a registered kind; pre_norm: x += mixer(norm(x)); x += ff(norm(x))  (compute.rs:204-336)

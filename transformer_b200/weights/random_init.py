@@ -23,34 +23,28 @@ from .loader import storage_dtype
 from .plan import Dest, TensorRule
 
 
-def _canonical_name(rule: TensorRule) -> str:
-    src = rule.canonical
-    if len(src.names) != 1:
-        raise ValueError(f"the canonical source of {rule.dest} must be one tensor")
-    return src.names[0]
-
-
-def _host_tensor(rule: TensorRule, seed: int, std: float) -> torch.Tensor:
-    shape = rule.canonical.shapes[0]
-    if rule.init == "ones":
-        return torch.ones(shape, dtype=torch.float32)
-    if rule.init == "normal":
+def _host_piece(name: str, shape, init: str, seed: int, std: float) -> torch.Tensor:
+    if init == "ones":
+        return torch.ones(tuple(shape), dtype=torch.float32)
+    if init == "normal":
         n = 1
         for s in shape:
             n *= int(s)
-        return torch.from_numpy(counter_random.normal_values(seed, _canonical_name(rule), 0, n, std)).view(*shape)
-    raise ValueError(f"unknown init {rule.init!r}")
+        return torch.from_numpy(counter_random.normal_values(seed, name, 0, n, std)).view(*shape)
+    raise ValueError(f"unknown init {init!r}")
 
 
 def random_file_tensors(rules: Sequence[TensorRule], seed: int, matrix_dtype: torch.dtype,
                         std: float = 0.02) -> Dict[str, torch.Tensor]:
-    """{file tensor name: CPU tensor} for the canonical source of every rule that owns storage."""
+    """{file tensor name: CPU tensor} for every tensor of the canonical source of every rule that owns storage
+    (a parameter may be joined from several file tensors: each is drawn under its own name)."""
     out: Dict[str, torch.Tensor] = {}
     for rule in rules:
         if rule.shared_with is not None:
             continue   # tied: the file holds no tensor of its own
-        t = _host_tensor(rule, int(seed), std)
-        out[_canonical_name(rule)] = t.to(storage_dtype(rule.role, matrix_dtype)).contiguous()
+        for name, shape in zip(rule.canonical.names, rule.canonical.shapes):
+            t = _host_piece(name, shape, rule.init, int(seed), std)
+            out[name] = t.to(storage_dtype(rule.role, matrix_dtype)).contiguous()
     return out
 
 
@@ -80,11 +74,15 @@ def random_device_weights(rules: Sequence[TensorRule], seed: int, compute_dtype:
                 continue
             if rule.init != "normal":
                 raise ValueError(f"unknown init {rule.init!r}")
-            if tuple(rule.canonical.shapes[0]) != tuple(rule.shape):
-                raise ValueError(f"{rule.dest}: the canonical file tensor and the parameter differ in shape")
-            t = torch.empty(rule.shape, dtype=dtype, device=device)
-            lib.random_fill(t, counter_random.stream_base(seed, _canonical_name(rule)),
-                            float(counter_random.scale_for(std)))
+            src = rule.canonical
+            pieces = []
+            for name, shape in zip(src.names, src.shapes):
+                t = torch.empty(tuple(shape), dtype=dtype, device=device)
+                lib.random_fill(t, counter_random.stream_base(seed, name), float(counter_random.scale_for(std)))
+                pieces.append(t)
+            t = src.combine(pieces).contiguous()
+            if tuple(t.shape) != tuple(rule.shape):
+                raise ValueError(f"{rule.dest}: the canonical file tensors do not join to the parameter's shape")
             out[rule.dest] = t
     for rule in rules:
         if rule.shared_with is not None:

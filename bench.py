@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the Llama-MoE engine on ONE B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --design salepel [--sizes s,m]      another design beside Llama-MoE at equal sizes (see bench_design)
 
 The default run has the layer sizes of the LLaMA-MoE-3.5B (4/16) shape (32 layers, width 4096,
 32/32 heads of 128, 16 experts top-4 of width 688, vocabulary 32000, context 4096) with random
@@ -142,6 +143,125 @@ def decode_bytes(c, distinct_experts_per_layer, context_tokens, elem=2):
     return fixed + experts + cache
 
 
+# ---- another design beside the closest existing model, at equal sizes (--design) ---------------------------------
+def design_shapes(size):
+    """(Salepel config, Llama-MoE config of equal width, depth, experts and attention output) for a named size."""
+    d, L, H, dim, rot, vdim, rank, q_rank, window, mh, mdim, mvdim, E, ident, top, ff = {
+        "s": (1024, 8, 8, 64, 32, 64, 256, 384, 1024, 4, 128, 256, 8, 1, 2, 512),
+        "m": (2048, 8, 16, 128, 64, 128, 512, 768, 2048, 8, 128, 256, 16, 2, 4, 704),
+    }[size]
+    att = {"heads": H, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "q_rank": q_rank,
+           "mask": {"size": window}, "rot": {"base": 10000.0, "dims": rot}, "scale": (dim + rot) ** -0.5}
+    mem = {"heads": mh, "dim": mdim, "vdim": mvdim, "gate_cap": 15.0}
+    mlp = {"kind": "moe", "router": {"experts": E, "identity": ident, "top": top}, "expert": {"ff": ff, "limit": 7.0}}
+    layers = []
+    for i in range(L):      # of four layers: a latent of its own, the matrix memory, two that read the first one's latent
+        if i % 4 == 1:
+            layers.append({"type": "mlstm", "mixer": mem, "mlp": mlp})
+        elif i % 4 == 0:
+            layers.append({"type": "latent_attention", "mixer": att, "mlp": mlp})
+        else:
+            layers.append({"type": "latent_attention", "mixer": dict(att, kv_from=i - i % 4), "mlp": mlp})
+    salepel = {"architecture": "Salepel", "vocab": 32000, "width": d, "norm": {"eps": 1e-6},
+               "embedding": {"scale": 1.0}, "max_context": 8192, "layers": layers}
+    llama = {"model_type": "llama", "num_hidden_layers": L, "hidden_size": d, "num_attention_heads": H * vdim // 128,
+             "num_key_value_heads": max(1, H * vdim // 128 // 4), "head_dim": 128, "intermediate_size": ff,
+             "num_local_experts": E, "num_experts_per_tok": top, "max_position_embeddings": 8192, "vocab_size": 32000,
+             "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "tie_word_embeddings": False}
+    return salepel, llama
+
+
+def bench_design(args):
+    """Prefill and decode throughput of the Salepel design beside a Llama-MoE of equal sizes, and the device time of
+    every kernel family in one eager step of each (CUDA events around each launch).  One JSON line."""
+    import torch
+    import transformer_b200 as tb
+    from transformer_b200.csrc import lib
+    from transformer_b200.sampling import Sampler
+
+    pk = peaks()
+    T, B, ctx0, K, W = args.prefill_tokens, args.batch, 1024, args.steps, max(3, args.warmup)
+    gen = torch.Generator().manual_seed(7)
+    out = {"metric": "prefill and decode tok/s, Salepel beside Llama-MoE at equal sizes", "unit": "tokens/s",
+           "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic: random weights, random token ids",
+           "peaks": pk, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx0, "steps": K, "warmup": W,
+           "sizes": {}}
+    for size in args.sizes.split(","):
+        row = {}
+        for name, cfg in zip(("salepel", "llama_moe"), design_shapes(size)):
+            room = max(T, B * (ctx0 + K * 8 + W + 80)) + 4096
+            engine = tb.random_model(cfg, seed=0, dtype=args.dtype, max_tokens=room, max_slots=B + 2,
+                                     max_step_tokens=max(8192, T))
+            V = engine.spec.vocab
+            sampler, greedy = Sampler(engine.device), tb.SampleArgs()
+            ptoks = torch.randint(0, V, (T,), generator=gen).tolist()
+            times = []
+            for i in range(W + 5):
+                s = engine.open()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                engine.step([s], [ptoks])
+                e1.record()
+                torch.cuda.synchronize()
+                engine.close(s)
+                if i >= W:
+                    times.append(e0.elapsed_time(e1))
+            p_ms = statistics.median(times)
+            engine.use_tapes = False
+            s = engine.open()
+            with lib.timing() as tp:
+                engine.step([s], [ptoks])
+            engine.close(s)
+            engine.use_tapes = True
+            # decode: B sequences of ctx0 tokens, one token each per step, sampled tokens stay on the device
+            slots = [engine.open() for _ in range(B)]
+            logits = engine.step(slots, [torch.randint(0, V, (ctx0,), generator=gen).tolist() for _ in range(B)])
+            ids = sampler.sample(logits, greedy)[0].clone()
+            shape = [[0]] * B
+
+            def one():
+                lg = engine.step(slots, shape, device_tokens=ids)
+                ids.copy_(sampler.sample(lg, greedy)[0])
+
+            engine.use_graphs, engine.use_tapes = False, False
+            one()
+            with lib.timing() as td:
+                one()
+            engine.use_graphs, engine.use_tapes = True, True
+            for _ in range(W):
+                one()
+            regions = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(K):
+                    one()
+                e1.record()
+                torch.cuda.synchronize()
+                regions.append(e0.elapsed_time(e1) / K)
+            d_ms = statistics.median(regions)
+            for sl in slots:
+                engine.close(sl)
+            weights = sum(t.numel() * t.element_size() for t in
+                          {id(t): t for p in [engine.embed, engine.head_part, engine.final_norm] +
+                           [q for l in engine.layers for q in l.parts().values()] for t in p.weights.values()}.values())
+            row[name] = {
+                "prefill_ms": p_ms, "prefill_tok_s": T / (p_ms * 1e-3), "decode_ms_per_step": d_ms,
+                "decode_tok_s": B / (d_ms * 1e-3), "weight_bytes": weights, "cache_bytes": engine.cache.nbytes,
+                "prefill_kernels_ms": {k: round(v, 4) for k, v in sorted(tp.ms.items(), key=lambda kv: -kv[1])},
+                "prefill_kernel_calls": tp.calls,
+                "decode_kernels_ms": {k: round(v, 4) for k, v in sorted(td.ms.items(), key=lambda kv: -kv[1])},
+                "decode_kernel_calls": td.calls,
+            }
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     global PROMPT_MIN, PROMPT_MAX, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
@@ -157,7 +277,16 @@ def main():
                     help="layer sizes: the benchmark's (default) or another shape BASELINE.json names")
     ap.add_argument("--prompt-max", type=int, default=0, help="longest prompt drawn (default: the shape's own)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
+    ap.add_argument("--design", default=None, choices=["salepel"],
+                    help="instead of the default workload: this design beside the closest existing model at equal "
+                         "sizes (prefill of --prefill-tokens, decode at --batch; sizes from --sizes)")
+    ap.add_argument("--sizes", default="s,m", help="with --design: which of the named sizes (s, m)")
     args = ap.parse_args()
+    if args.design is not None and args.impl == "ours":
+        if args.gpus != 1:
+            print(f"bench.py measures one GPU only (asked for {args.gpus})")
+            return 2
+        return bench_design(args)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

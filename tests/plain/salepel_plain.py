@@ -173,15 +173,21 @@ def expert(h: torch.Tensor, gate_w, up_w, down_w, limit: float, store=None) -> t
     return st(g * torch.sigmoid(GLU_ALPHA * g) * (u + 1.0)) @ down_w.T
 
 
-def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], f: dict, store=None, forced=None) -> torch.Tensor:
-    """h [n, d] -> [n, d].  Outputs E .. E + identity - 1 of the router stand for experts whose output is h."""
+def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], f: dict, store=None, forced=None, margins_out=None) -> torch.Tensor:
+    """h [n, d] -> [n, d].  Outputs E .. E + identity - 1 of the router stand for experts whose output is h.
+    ``forced`` [n, top]: the experts to use instead of the free choice; ``margins_out`` then receives, per token,
+    (free choice, gap between the last chosen and the first left-out choice score)."""
     st = store or (lambda z: z)
-    E, ident, top = f["router"]["experts"], f["router"]["identity"], f["router"]["top"]
+    E, ident, top = f["router"]["experts"], f["router"].get("identity", 0), f["router"]["top"]
     limit = float(f["expert"]["limit"])
-    idx, wt, _ = route(h, w, top)
+    idx, wt, s = route(h, w, top)
+    if margins_out is not None:
+        choice = torch.sort(s + w["correction"], dim=-1, descending=True).values
+        gaps = choice[:, top - 1] - choice[:, top] if choice.shape[1] > top else torch.full((h.shape[0],), 1e9)
+        margins_out.append([(sorted(int(e) for e in idx[t]), float(gaps[t])) for t in range(h.shape[0])])
     if forced is not None:
         idx = forced
-        wt = torch.gather(route(h, w, top)[2], 1, idx)
+        wt = torch.gather(s, 1, idx)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(top):
@@ -202,9 +208,10 @@ def sub(tensors: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor
 
 
 def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int], store=None, layers_out=None,
-            routes=None) -> torch.Tensor:
+            routes=None, margins_out=None) -> torch.Tensor:
     """Logits [n, vocab] of one whole sequence.  ``layers_out``: a list that receives the stream after every
-    layer; ``routes``: {layer: index [n, top]} forces the experts' choice."""
+    layer; ``routes``: {layer: index [n, top]} forces the experts' choice; ``margins_out``: a dict that receives
+    {layer: [(free choice, gap) per token]}."""
     eps = cfg["norm"]["eps"]
     x = embedding(tensors["embed"], tokens, cfg["embedding"]["scale"])
     latents = {}
@@ -229,7 +236,13 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int], 
         if layer.get("mlp") is not None:
             h = rms_norm(x, tensors[p + "norm2"], eps)
             h = store(h) if store else h
-            y = moe(h, sub(tensors, p + "mlp."), layer["mlp"], store, None if routes is None else routes.get(i))
+            margins = None
+            if margins_out is not None:
+                margins = []
+            y = moe(h, sub(tensors, p + "mlp."), layer["mlp"], store, None if routes is None else routes.get(i),
+                    margins)
+            if margins_out is not None:
+                margins_out[i] = margins[0]
             x = x + rms_norm(y, tensors[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())

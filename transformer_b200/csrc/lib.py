@@ -54,6 +54,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_mlstm_scan_f32": "pppppppiiiiiff", "tb_mlstm_scan_bf16": "pppppppiiiiiff",
     "tb_mlstm_out_f32": "ppippiiif", "tb_mlstm_out_bf16": "ppippiiif",
     "tb_latent_prep_f32": "pippfpppppippiiiii", "tb_latent_prep_bf16": "pippfpppppippiiiii",
+    "tb_latent_attention_mma_bf16": "ppppppppppppiiiiiiiiiiif",
     "tb_latent_attention_f32": "pppppppppppiiiiiiiiiif", "tb_latent_attention_bf16": "pppppppppppiiiiiiiiiif",
 }
 class TapeArg(ctypes.Union):
@@ -174,6 +175,41 @@ class recording:
         return False
 
 
+_timing = None        # while launches are timed: launcher name -> [(start event, end event)]
+
+
+class timing:
+    """``with timing() as t:`` every launcher call inside is bracketed by CUDA events on the launching stream;
+    afterwards ``t.ms`` holds the device time per launcher name, ``t.calls`` the number of calls.  For eager steps
+    (a replayed graph or tape calls no launcher from Python); costs two event records per launch."""
+
+    def __enter__(self):
+        global _timing
+        self._before = _timing
+        _timing = self._events = {}
+        self.ms, self.calls = {}, {}
+        return self
+
+    def __exit__(self, *exc):
+        global _timing
+        _timing = self._before
+        torch.cuda.synchronize()
+        for name, pairs in self._events.items():
+            self.ms[name] = sum(a.elapsed_time(b) for a, b in pairs)
+            self.calls[name] = len(pairs)
+        return False
+
+
+def _timed(name, fn, args):
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    rc = fn(*args, _stream())
+    b.record()
+    if rc == 0:
+        _timing.setdefault(name, []).append((a, b))
+    return rc
+
+
 def foreign(kind: str, *tensors) -> None:
     """Tell a recording that device work of another kind is about to run here (a library product, ...)."""
     if _recorder is not None:
@@ -185,7 +221,7 @@ def try_call(name: str, *args) -> bool:
     instead of raising, so the caller can take the general kernel."""
     global launch_count
     fn = getattr(_lib if _lib is not None else library(), name)
-    rc = fn(*args, _stream())
+    rc = fn(*args, _stream()) if _timing is None else _timed(name, fn, args)
     if rc == -2:
         return False
     if rc != 0:
@@ -201,7 +237,7 @@ def call(name: str, *args) -> None:
     global launch_count
     launch_count += 1
     fn = getattr(_lib if _lib is not None else library(), name)
-    rc = fn(*args, _stream())
+    rc = fn(*args, _stream()) if _timing is None else _timed(name, fn, args)
     if rc != 0:
         raise KernelError(f"{name}: {_error_text(rc)}")
     if _recorder is not None:

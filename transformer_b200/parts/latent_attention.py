@@ -22,6 +22,9 @@ from .linear import batched_matmul, matmul_nt
 from .spec import PartSpec
 
 
+USE_TENSOR_CORES = True    # bfloat16: the mma.sync kernel before the general one
+
+
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
     """params: width, heads, dim, rot_dim, vdim, kv_rank, q_rank, window, scale, eps, own_latent, position (a
@@ -99,10 +102,23 @@ class LatentAttention(Mixer):
         batched_matmul(q.view(nt, H, self.q_head)[:, :, :self.dim], w["ukT"], qa)
         ol = ctx.scratch("latent.ol", (nt, H, self.rank), self.dtype)
         tiles = ctx.tiles(self.tile)
-        lib.call("tb_latent_attention_" + sfx, lib.ptr(qa), lib.ptr(q), lib.ptr(ol), lib.ptr(cache.kv),
-                 lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos), lib.ptr(table),
-                 lib.ptr(cos), lib.ptr(sin), tiles.count, ctx.max_pages, H * self.q_head, self.q_head, self.dim, H,
-                 self.rank, self.rot, self.rdims, self.window, self.scale)
+        done = False
+        if self.dtype == torch.bfloat16 and USE_TENSOR_CORES:
+            # Slices of the key range, so that a few sequences still fill the GPU: a function of the batch's shape
+            # alone (a captured graph keeps it), at most one slice per page of the window
+            blocks = tiles.count * ((H + 15) // 16)
+            splits = int(max(1, min(16, (self.window + 63) // 64 + 1, (2 * ctx.engine.sm_count) // max(1, blocks))))
+            partial = ctx.scratch("latent.partial", (nt, H, splits, self.rank + 2), torch.float32) if splits > 1 else None
+            done = lib.try_call("tb_latent_attention_mma_bf16", lib.ptr(qa), lib.ptr(q), lib.ptr(ol), lib.ptr(partial),
+                                lib.ptr(cache.kv), lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq),
+                                lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(cos), lib.ptr(sin), tiles.count, nt,
+                                ctx.max_pages, H * self.q_head, self.q_head, H, self.rank, self.rot, self.rdims,
+                                self.window, splits, self.scale)
+        if not done:
+            lib.call("tb_latent_attention_" + sfx, lib.ptr(qa), lib.ptr(q), lib.ptr(ol), lib.ptr(cache.kv),
+                     lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos), lib.ptr(table),
+                     lib.ptr(cos), lib.ptr(sin), tiles.count, ctx.max_pages, H * self.q_head, self.q_head, self.dim, H,
+                     self.rank, self.rot, self.rdims, self.window, self.scale)
         o = ctx.scratch("latent.o", (nt, H, self.vdim), self.dtype)
         batched_matmul(ol, w["uv"].view(H, self.vdim, self.rank), o)
         matmul_nt(o.view(nt, H * self.vdim), w["wo"], out)

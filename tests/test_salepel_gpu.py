@@ -310,9 +310,10 @@ def test_tensor_core_attention_kernel_at_every_edge(H, rank, rot, window, splits
         assert float((got - want).abs().max()) <= 2e-2, f"{which}: {float((got - want).abs().max()):.3e}"
 
 
+@pytest.mark.parametrize("kernel", ["scan", "chunk"])
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H, dim, vdim", [(2, 16, 24), (1, 40, 70), (3, 128, 33)])
-def test_matrix_memory_kernel_keeps_a_token_for_hundreds_of_steps(dtype, H, dim, vdim):
+@pytest.mark.parametrize("H, dim, vdim", [(2, 16, 24), (1, 40, 70), (3, 128, 33), (2, 64, 64), (1, 256, 32)])
+def test_matrix_memory_kernel_keeps_a_token_for_hundreds_of_steps(dtype, H, dim, vdim, kernel):
     """Gates made so that one early token is written at full strength and (almost) nothing is forgotten: asked with
     that token's key hundreds of tokens later, in a later step and in a slot used before, the answer is its value."""
     from transformer_b200.csrc import lib
@@ -340,7 +341,8 @@ def test_matrix_memory_kernel_keeps_a_token_for_hundreds_of_steps(dtype, H, dim,
     sfx = "f32" if dtype == "float32" else "bf16"
     I = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
     dq, dg, db, starts1, starts2 = _dev(qkv), _dev(gates), _dev(bias), I([0, lens[0], nt]), I([0, 1, 2])
-    lib.call("tb_mlstm_scan_" + sfx, lib.ptr(dq), lib.ptr(dg), lib.ptr(db), lib.ptr(state), lib.ptr(out),
+    # the prompts token by token or 64 tokens at a time (300 = four chunks and a part of one); the last token alone
+    lib.call(f"tb_mlstm_{kernel}_" + sfx, lib.ptr(dq), lib.ptr(dg), lib.ptr(db), lib.ptr(state), lib.ptr(out),
              lib.ptr(starts1), lib.ptr(slots), B, ld, H, dim, vdim, cap, dim ** -0.5)
     lib.call("tb_mlstm_scan_" + sfx, lib.ptr(dq[nt:]), lib.ptr(dg[nt:]), lib.ptr(db), lib.ptr(state),
              lib.ptr(out[nt:]), lib.ptr(starts2), lib.ptr(slots), B, ld, H, dim, vdim, cap, dim ** -0.5)

@@ -88,6 +88,7 @@ template <typename T> struct RouterTail {
     int E, k;
     int* idx;          // [rows, k]
     float* wts;        // [rows, k]
+    RouterRule rule;   // how the logits become a choice
 };
 
 template <typename T, int NORM_THREADS, bool EARLY, bool TAIL>
@@ -95,7 +96,9 @@ __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ wy,
                        const int* __restrict__ pair_row, const float* __restrict__ topk_w, int k,
                        const int* __restrict__ rows, const float* __restrict__ w, float eps, T* __restrict__ y,
-                       int d, const void* warm, int warm_bytes, const RouterTail<T> tail) {
+                       int d, const void* warm, int warm_bytes, const RouterTail<T> tail,
+                       const float* __restrict__ post_w, float post_eps) {
+    // post_w: the delta is normed by itself first (delta / rms(delta) * post_w, with post_eps) and then added
     constexpr int EPL = Vec16<T>::N, UN = 8;
     extern __shared__ __align__(16) unsigned char tail_smem[];      // TAIL: the row as T [d], then logits [E]
     uint4 first[TAIL ? UN : 1];
@@ -131,10 +134,51 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
     const bool write_back = (rows == nullptr) && has_delta;
     float v[NORM_CHUNKS][8];
     float ss = 0.f;
+    if (post_w) {
+        float ss1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < NORM_CHUNKS; ++j) {
+            const int c = (threadIdx.x + j * NORM_THREADS) * 8;
+            if (c < d) {
+                if (dr) {
+                    load8(dr + c, v[j]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[j][e] = 0.f;
+                    for (int q = 0; q < k; ++q) {
+                        float t[8];
+                        load8(wy + (size_t)pair_row[(size_t)r * k + q] * d + c, t);
+                        const float wq = topk_w[(size_t)r * k + q];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[j][e] += wq * t[e];
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss1 += v[j][e] * v[j][e];
+            }
+        }
+        ss1 = block_sum(ss1, red);
+        const float rs1 = 1.0f / sqrtf(ss1 / (float)d + post_eps);
+#pragma unroll
+        for (int j = 0; j < NORM_CHUNKS; ++j) {
+            const int c = (threadIdx.x + j * NORM_THREADS) * 8;
+            if (c < d) {
+                float xv[8], pw[8];
+                load8(xr + c, xv);
+                load8(post_w + c, pw);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    v[j][e] = xv[e] + v[j][e] * rs1 * pw[e];
+                    ss += v[j][e] * v[j][e];
+                }
+                if (write_back) store8(xr + c, v[j]);
+            }
+        }
+    }
 #pragma unroll
     for (int j = 0; j < NORM_CHUNKS; ++j) {
         const int c = (threadIdx.x + j * NORM_THREADS) * 8;
-        if (c < d) {
+        if (c < d && !post_w) {
             load8(xr + c, v[j]);
             if (dr) {
                 float t[8];
@@ -158,6 +202,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
             for (int e = 0; e < 8; ++e) ss += v[j][e] * v[j][e];
         }
     }
+    if (!y) return;                 // the sum alone
     ss = block_sum(ss, red);
     const float rs = 1.0f / sqrtf(ss / (float)d + eps);
     T* yr = y + (size_t)i * d;
@@ -206,7 +251,13 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
         if (lane == 0) lg[e] = acc;
     }
     __syncthreads();
-    if (warp == 0) router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
+    if (warp == 0) {
+        if (tail.rule.scored)
+            router_pick_scored(lg, lg + tail.E, tail.rule.bias, tail.idx + (size_t)i * tail.k,
+                               tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
+        else
+            router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
+    }
 }
 
 template <typename T>
@@ -238,9 +289,9 @@ __global__ void __launch_bounds__(256)
 post_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ wy,
                         const int* __restrict__ pair_row, const float* __restrict__ topk_w, int k,
                         const float* __restrict__ post_w, float post_eps, const int* __restrict__ rows,
-                        const float* __restrict__ w, float eps, T* __restrict__ y, int d) {
+                        const float* __restrict__ w, float eps, T* __restrict__ y, int d, const RouterTail<T> tail) {
     pdl_sync();
-    extern __shared__ float row[];
+    extern __shared__ float row[];      // [d], and with a router tail its logits (and scores) behind
     __shared__ float red[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -272,21 +323,30 @@ post_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, cons
     ss2 = block_sum(ss2, red);
     const float rs2 = 1.0f / sqrtf(ss2 / (float)d + eps);
     T* yr = y + (size_t)i * d;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) stf(yr + c, row[c] * rs2 * w[c]);
-}
-
-template <typename T>
-static int post_add_rmsnorm_launch(float* x, const void* delta, const void* wy, const int* pair_row,
-                                   const float* topk_w, int k, const float* post_w, float post_eps, const int* rows,
-                                   const float* w, float eps, void* y, int n_out, int d, cudaStream_t s) {
-    if (n_out < 0 || d <= 0 || !post_w || (y && !w)) return TB_ERR_ARG;
-    if ((delta == nullptr) == (wy == nullptr)) return TB_ERR_ARG;
-    if (wy && (!pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
-    if ((size_t)d * sizeof(float) > 48 * 1024) return TB_ERR_UNSUPPORTED;
-    if (n_out == 0) return 0;
-    TB_LAUNCH((post_add_rmsnorm_kernel<T>), n_out, 256, (size_t)d * sizeof(float), s, x, (const T*)delta, (const T*)wy,
-              pair_row, topk_w, k, post_w, post_eps, rows, w, eps, (T*)y, d);
-    return tb_last_error();
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        stf(yr + c, row[c] * rs2 * w[c]);
+        if (tail.w) row[c] = ldf(yr + c);       // what the router reads: the row as stored
+    }
+    if (!tail.w) return;
+    // the router of the row just normed, by the rules of router_kernel: a warp per output, one warp picks
+    __syncthreads();
+    float* lg = row + d;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int e = warp; e < tail.E; e += nw) {
+        const T* we = tail.w + (size_t)e * d;
+        float acc = 0.f;
+        for (int c = lane; c < d; c += 32) acc += row[c] * ldf(we + c);
+        acc = warp_sum(acc);
+        if (lane == 0) lg[e] = acc;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        if (tail.rule.scored)
+            router_pick_scored(lg, lg + tail.E, tail.rule.bias, tail.idx + (size_t)i * tail.k,
+                               tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
+        else
+            router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
+    }
 }
 
 template <typename T>
@@ -303,34 +363,62 @@ template <typename T>
 static int add_rmsnorm_launch(float* x, const void* delta, const void* wy, const int* pair_row,
                               const float* topk_w, int k, const int* rows, const float* w, float eps,
                               void* y, int n_out, int d, const void* warm, int warm_bytes, cudaStream_t s,
-                              RouterTail<T> tail = RouterTail<T>{nullptr, 0, 0, nullptr, nullptr}) {
+                              RouterTail<T> tail = RouterTail<T>{nullptr, 0, 0, nullptr, nullptr, RouterRule{0, nullptr}},
+                              const float* post_w = nullptr, float post_eps = 0.f) {
     if (n_out < 0 || d <= 0) return TB_ERR_ARG;
+    if (post_w && !delta && !wy) return TB_ERR_ARG;
+    if (!y && (!post_w || tail.w)) return TB_ERR_ARG;
     if (wy && (delta || !pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
     if (tail.w && (tail.E <= 0 || tail.k <= 0 || tail.k > tail.E || !tail.idx || !tail.wts)) return TB_ERR_ARG;
     if (n_out == 0) return 0;
     if (tail.w) {
         // the form that also routes: a few rows, a width of 16-byte pieces, the row and the logits in 40 KB
-        const size_t smem = (size_t)d * sizeof(T) + (size_t)tail.E * sizeof(float);
+        const size_t smem = (size_t)d * sizeof(T) + (size_t)tail.E * sizeof(float) * (tail.rule.scored ? 2 : 1);
         if (d % 8 || d > 512 * 8 * NORM_CHUNKS || n_out > 256 || smem > 40 * 1024 ||
             (reinterpret_cast<uintptr_t>(tail.w) & 15))
             return TB_ERR_UNSUPPORTED;           // the caller runs the router by itself
         TB_LAUNCH((add_rmsnorm_vec_kernel<T, 512, true, true>), n_out, 512, smem, s, x, (const T*)delta, (const T*)wy,
-                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, nullptr, 0, tail);
+                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, nullptr, 0, tail, post_w, post_eps);
         return tb_last_error();
     }
-    if (d % 8 == 0 && n_out <= 256 && d <= 512 * 8 * NORM_CHUNKS) {
+    if (d % 8 == 0 && n_out <= 256 && d <= 512 * 8 * NORM_CHUNKS && y) {
         TB_LAUNCH((add_rmsnorm_vec_kernel<T, 512, true, false>), n_out, 512, 0, s, x, (const T*)delta, (const T*)wy,
-                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes, tail);
+                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes, tail, post_w, post_eps);
         return tb_last_error();
     }
     if (d % 8 == 0 && d <= 256 * 8 * NORM_CHUNKS) {
         TB_LAUNCH((add_rmsnorm_vec_kernel<T, 256, false, false>), n_out, 256, 0, s, x, (const T*)delta, (const T*)wy,
-                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes, tail);
+                  pair_row, topk_w, k, rows, w, eps, (T*)y, d, warm, warm_bytes, tail, post_w, post_eps);
         return tb_last_error();
     }
+    if (post_w) return TB_ERR_UNSUPPORTED;      // the caller takes the kernel that keeps the row in shared memory
     int threads = d >= 2048 ? 512 : 256;
     TB_LAUNCH((add_rmsnorm_kernel<T>), n_out, threads, 0, s, x, (const T*)delta, (const T*)wy, pair_row, topk_w, k, rows, w, eps,
                                                    (T*)y, d, warm, warm_bytes);
+    return tb_last_error();
+}
+
+template <typename T>
+static int post_add_rmsnorm_launch(float* x, const void* delta, const void* wy, const int* pair_row,
+                                   const float* topk_w, int k, const float* post_w, float post_eps, const int* rows,
+                                   const float* w, float eps, void* y, int n_out, int d, cudaStream_t s,
+                                   RouterTail<T> tail = RouterTail<T>{nullptr, 0, 0, nullptr, nullptr,
+                                                                      RouterRule{0, nullptr}}) {
+    if (n_out < 0 || d <= 0 || !post_w || (y && !w)) return TB_ERR_ARG;
+    if ((delta == nullptr) == (wy == nullptr)) return TB_ERR_ARG;
+    if (wy && (!pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
+    if (tail.w && (!y || tail.E <= 0 || tail.k <= 0 || tail.k > tail.E || !tail.idx || !tail.wts)) return TB_ERR_ARG;
+    const size_t smem = ((size_t)d + (tail.w ? 2 * (size_t)tail.E : 0)) * sizeof(float);
+    if (smem > 48 * 1024) return TB_ERR_UNSUPPORTED;
+    if (n_out == 0) return 0;
+    {
+        // the forms that keep the row in registers and move 16 bytes at a time, for the widths they take
+        const int rc = add_rmsnorm_launch<T>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, nullptr, 0, s,
+                                             tail, post_w, post_eps);
+        if (rc != TB_ERR_UNSUPPORTED) return rc;
+    }
+    TB_LAUNCH((post_add_rmsnorm_kernel<T>), n_out, 256, smem, s, x, (const T*)delta, (const T*)wy,
+              pair_row, topk_w, k, post_w, post_eps, rows, w, eps, (T*)y, d, tail);
     return tb_last_error();
 }
 
@@ -361,6 +449,21 @@ int tb_post_add_rmsnorm_bf16(float* x, const void* delta, const void* wy, const 
     return post_add_rmsnorm_launch<__nv_bfloat16>(x, delta, wy, pair_row, topk_w, k, post_w, post_eps, rows, w, eps,
                                                   y, n_out, d, s);
 }
+// The same, and the router of the rows just normed in the same kernel (router_w [E, d]; scored: the rule of
+// tb_router_scored_*, with bias [E] or null; else the rule of tb_router_*).
+#define TB_POST_ROUTER(NAME, T)                                                                                      \
+    int NAME(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w, int k,           \
+             const float* post_w, float post_eps, const float* w, float eps, void* y, const void* router_w,          \
+             const float* bias, int* route_idx, float* route_w, int n_out, int d, int E, int route_k, int scored,    \
+             cudaStream_t s) {                                                                                       \
+        if (!router_w) return TB_ERR_ARG;                                                                            \
+        return post_add_rmsnorm_launch<T>(x, delta, wy, pair_row, topk_w, k, post_w, post_eps, nullptr, w, eps, y,   \
+                                          n_out, d, s,                                                               \
+                                          RouterTail<T>{(const T*)router_w, E, route_k, route_idx, route_w,          \
+                                                        RouterRule{scored, bias}});                                  \
+    }
+TB_POST_ROUTER(tb_post_add_rmsnorm_router_f32, float)
+TB_POST_ROUTER(tb_post_add_rmsnorm_router_bf16, __nv_bfloat16)
 // warm / warm_bytes: weights that the next kernel reads first, to be asked into L2 meanwhile (or null / 0).
 int tb_add_rmsnorm_f32(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w, int k,
                        const int* rows, const float* w, float eps, void* y, int n_out, int d, const void* warm,
@@ -381,7 +484,8 @@ int tb_add_rmsnorm_router_f32(float* x, const void* delta, const void* wy, const
                               int* route_idx, float* route_w, int n_out, int d, int E, int route_k, cudaStream_t s) {
     if (!router_w) return TB_ERR_ARG;
     return add_rmsnorm_launch<float>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, nullptr, 0, s,
-                                     RouterTail<float>{(const float*)router_w, E, route_k, route_idx, route_w});
+                                     RouterTail<float>{(const float*)router_w, E, route_k, route_idx, route_w,
+                                                       RouterRule{0, nullptr}});
 }
 int tb_add_rmsnorm_router_bf16(float* x, const void* delta, const void* wy, const int* pair_row, const float* topk_w,
                                int k, const int* rows, const float* w, float eps, void* y, const void* router_w,
@@ -389,7 +493,27 @@ int tb_add_rmsnorm_router_bf16(float* x, const void* delta, const void* wy, cons
     if (!router_w) return TB_ERR_ARG;
     return add_rmsnorm_launch<__nv_bfloat16>(
         x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, nullptr, 0, s,
-        RouterTail<__nv_bfloat16>{(const __nv_bfloat16*)router_w, E, route_k, route_idx, route_w});
+        RouterTail<__nv_bfloat16>{(const __nv_bfloat16*)router_w, E, route_k, route_idx, route_w,
+                                  RouterRule{0, nullptr}});
+}
+// The same with the scored rule of choice (softmax over all outputs, the largest of score + bias, weights = scores).
+int tb_add_rmsnorm_router_scored_f32(float* x, const void* delta, const void* wy, const int* pair_row,
+                                     const float* topk_w, int k, const int* rows, const float* w, float eps, void* y,
+                                     const void* router_w, const float* bias, int* route_idx, float* route_w, int n_out,
+                                     int d, int E, int route_k, cudaStream_t s) {
+    if (!router_w) return TB_ERR_ARG;
+    return add_rmsnorm_launch<float>(x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, nullptr, 0, s,
+                                     RouterTail<float>{(const float*)router_w, E, route_k, route_idx, route_w,
+                                                       RouterRule{1, bias}});
+}
+int tb_add_rmsnorm_router_scored_bf16(float* x, const void* delta, const void* wy, const int* pair_row,
+                                      const float* topk_w, int k, const int* rows, const float* w, float eps, void* y,
+                                      const void* router_w, const float* bias, int* route_idx, float* route_w,
+                                      int n_out, int d, int E, int route_k, cudaStream_t s) {
+    if (!router_w) return TB_ERR_ARG;
+    return add_rmsnorm_launch<__nv_bfloat16>(
+        x, delta, wy, pair_row, topk_w, k, rows, w, eps, y, n_out, d, nullptr, 0, s,
+        RouterTail<__nv_bfloat16>{(const __nv_bfloat16*)router_w, E, route_k, route_idx, route_w, RouterRule{1, bias}});
 }
 }
 
@@ -401,7 +525,11 @@ TB_TAPE_REGISTER(tb_embed_scaled_f32)
 TB_TAPE_REGISTER(tb_embed_scaled_bf16)
 TB_TAPE_REGISTER(tb_post_add_rmsnorm_f32)
 TB_TAPE_REGISTER(tb_post_add_rmsnorm_bf16)
+TB_TAPE_REGISTER(tb_post_add_rmsnorm_router_f32)
+TB_TAPE_REGISTER(tb_post_add_rmsnorm_router_bf16)
 TB_TAPE_REGISTER(tb_add_rmsnorm_f32)
 TB_TAPE_REGISTER(tb_add_rmsnorm_bf16)
 TB_TAPE_REGISTER(tb_add_rmsnorm_router_f32)
 TB_TAPE_REGISTER(tb_add_rmsnorm_router_bf16)
+TB_TAPE_REGISTER(tb_add_rmsnorm_router_scored_f32)
+TB_TAPE_REGISTER(tb_add_rmsnorm_router_scored_bf16)

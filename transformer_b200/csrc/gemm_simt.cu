@@ -154,6 +154,37 @@ static int gemm_simt_launch(const GemmArgs& a, cudaStream_t s, int batches = 1) 
     return tb_last_error();
 }
 
+// A few rows against one matrix per batch (decoding: the heads of a mixer whose heads have matrices of their own):
+// C[m, b, n] = sum_k A[m, b, k] B[b, n, k].  One warp per output column streams that column's row of B once (its
+// lanes stride over k) and keeps one sum per row of A; A is small and comes from cache.  Up to BR_ROWS rows.
+#define BR_ROWS 16
+template <typename T>
+__global__ void __launch_bounds__(256)
+batched_rows_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, long long a_stride,
+                    long long b_stride, long long c_stride, int lda, int ldb, int ldc, int M, int N, int K) {
+    pdl_sync();
+    const int lane = threadIdx.x & 31, n = blockIdx.x * 8 + (threadIdx.x >> 5), b = blockIdx.y;
+    if (n >= N) return;
+    const T* Bn = B + (size_t)b * b_stride + (size_t)n * ldb;
+    const T* Ab = A + (size_t)b * a_stride;
+    float acc[BR_ROWS];
+#pragma unroll
+    for (int m = 0; m < BR_ROWS; ++m) acc[m] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float w = ldf(Bn + k);
+#pragma unroll
+        for (int m = 0; m < BR_ROWS; ++m)
+            if (m < M) acc[m] += w * ldf(Ab + (size_t)m * lda + k);
+    }
+#pragma unroll
+    for (int m = 0; m < BR_ROWS; ++m) {
+        if (m < M) {
+            const float v = warp_sum(acc[m]);
+            if (lane == 0) stf(C + (size_t)b * c_stride + (size_t)m * ldc + n, v);
+        }
+    }
+}
+
 extern "C" {
 // out_kind: 0 = C has the type of A and B, 1 = C is float, 2 = swiglu pair (C has the type of A)
 #define TB_GEMM(NAME, T)                                                                                        \
@@ -188,6 +219,11 @@ TB_GEMM_GLU(tb_gemm_simt_glu_bf16, __nv_bfloat16)
 #define TB_GEMM_BATCHED(NAME, T)                                                                                \
     int NAME(const void* A, const void* B, void* C, long long a_stride, long long b_stride, long long c_stride, \
              int lda, int ldb, int ldc, int M, int N, int K, int batches, cudaStream_t s) {                     \
+        if (M > 0 && M <= BR_ROWS && N > 0 && K > 0 && batches > 0 && batches <= 65535) {                       \
+            TB_LAUNCH((batched_rows_kernel<T>), dim3((N + 7) / 8, batches), 256, 0, s, (const T*)A, (const T*)B, (T*)C, \
+                      a_stride, b_stride, c_stride, lda, ldb, ldc, M, N, K);                                    \
+            return tb_last_error();                                                                             \
+        }                                                                                                       \
         GemmArgs a{A, nullptr, B, C, nullptr, b_stride, lda, ldb, ldc, M, N, K, 1, GluRule{0, 0.f, 0.f},        \
                    a_stride, c_stride};                                                                         \
         return gemm_simt_launch<T, T, false>(a, s, batches);                                                    \

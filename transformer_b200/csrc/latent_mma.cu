@@ -77,18 +77,25 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
     const int seq = a.tile_seq[tile], t0 = a.tile_t0[tile];
     const int hc = a.heads_per_block;
     const int n_tok = min(a.tile_nq[tile], a.tokens_per_block);
-    // ---- queries: the latent's side as it is, the rotated part rotated here, both unscaled ----------------
-    for (int idx = threadIdx.x; idx < LM_ROWS * DK; idx += blockDim.x) {
-        const int row = idx / DK, c = idx - row * DK;
-        const int ti = row / hc, h = h0 + row % hc;
-        float v = 0.f;
-        if (ti < n_tok && h < a.H) {
-            const int t = t0 + ti;
-            if (c < a.rank) {
-                v = __bfloat162float(a.qa[((size_t)t * a.H + h) * a.rank + c]);
-            } else {
+    // ---- queries: the latent's side as it is (16 bytes at a time), the rotated part rotated here, both unscaled ----
+    {
+        const int chunks_q = a.rank / 8;
+        for (int idx = threadIdx.x; idx < LM_ROWS * chunks_q; idx += blockDim.x) {
+            const int row = idx / chunks_q, c = (idx - row * chunks_q) * 8;
+            const int ti = row / hc, h = h0 + row % hc;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (ti < n_tok && h < a.H)
+                v = *reinterpret_cast<const uint4*>(a.qa + ((size_t)(t0 + ti) * a.H + h) * a.rank + c);
+            *reinterpret_cast<uint4*>(q_s + row * pitch + c) = v;
+        }
+        for (int idx = threadIdx.x; idx < LM_ROWS * a.rot; idx += blockDim.x) {
+            const int row = idx / a.rot, r = idx - row * a.rot;
+            const int ti = row / hc, h = h0 + row % hc;
+            float v = 0.f;
+            if (ti < n_tok && h < a.H) {
+                const int t = t0 + ti;
                 const __nv_bfloat16* qr = a.q + (size_t)t * a.ldq + (size_t)h * a.q_head + a.q_plain;
-                const int r = c - a.rank, half = a.rdims / 2, pos = a.tok_pos[t];
+                const int half = a.rdims / 2, pos = a.tok_pos[t];
                 v = __bfloat162float(qr[r]);
                 if (r < half) {
                     const float co = a.cosT[(size_t)pos * half + r], si = a.sinT[(size_t)pos * half + r];
@@ -98,8 +105,8 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
                     v = v * co + __bfloat162float(qr[r - half]) * si;
                 }
             }
+            q_s[row * pitch + a.rank + r] = __float2bfloat16_rn(v);
         }
-        q_s[row * pitch + c] = __float2bfloat16_rn(v);
     }
     if (threadIdx.x < LM_ROWS) {
         const int ti = threadIdx.x / hc, h = h0 + threadIdx.x % hc;
@@ -252,29 +259,33 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
     }
 }
 
-// out[t, h] = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s        one warp per (token, head)
+// out[t, h] = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s        one block per (token, head): the slices' factors
+// once, then every thread its columns with the loads of all slices in flight together
+#define LM_MAX_SPLITS 16
 __global__ void __launch_bounds__(128)
-latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int rows, int splits, int rank) {
+latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int splits, int rank) {
     pdl_sync();
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const float* p = partial + (size_t)row * splits * (rank + 2);
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, p[(size_t)s * (rank + 2)]);
-    float l = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = p[(size_t)s * (rank + 2)];
-        if (ms > -INFINITY) l += __expf(ms - m) * p[(size_t)s * (rank + 2) + 1];
+    __shared__ float f_s[LM_MAX_SPLITS];
+    const float* p = partial + (size_t)blockIdx.x * splits * (rank + 2);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float ms = lane < splits ? p[(size_t)lane * (rank + 2)] : -INFINITY;
+        const float ls = lane < splits ? p[(size_t)lane * (rank + 2) + 1] : 0.f;
+        const float m = warp_max(ms);
+        const float f = ms > -INFINITY ? __expf(ms - m) : 0.f;
+        const float l = warp_sum(f * ls);
+        if (lane < splits) f_s[lane] = l > 0.f ? f / l : 0.f;
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    for (int c = lane; c < rank; c += 32) {
-        float v = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = p[(size_t)s * (rank + 2)];
-            if (ms > -INFINITY) v += __expf(ms - m) * p[(size_t)s * (rank + 2) + 2 + c];
-        }
-        out[(size_t)row * rank + c] = __float2bfloat16_rn(v * inv);
+    __syncthreads();
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float v[LM_MAX_SPLITS];
+#pragma unroll
+        for (int s = 0; s < LM_MAX_SPLITS; ++s) v[s] = s < splits ? p[(size_t)s * (rank + 2) + 2 + c] : 0.f;
+        float acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < LM_MAX_SPLITS; ++s)
+            if (s < splits) acc += f_s[s] * v[s];
+        out[(size_t)blockIdx.x * rank + c] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -301,9 +312,10 @@ int tb_latent_attention_mma_bf16(const void* qa, const void* q, void* out, float
                                  int splits, float scale, cudaStream_t s) {
     const int q_plain = q_head - rot;      // a head's queries: the plain entries, then the rotated ones
     if (tiles < 0 || nt < 0 || H <= 0 || rank <= 0 || rot < 0 || window <= 0 || rdims < 0 || rdims > rot || rdims % 2 ||
-        splits < 1 || (splits > 1 && !partial))
+        splits < 1 || splits > LM_MAX_SPLITS || (splits > 1 && !partial))
         return TB_ERR_ARG;
-    if (rank % 32 || rank > 512 || (rank + rot) % 16 || (((uintptr_t)cache) & 15)) return TB_ERR_UNSUPPORTED;
+    if (rank % 32 || rank > 512 || (rank + rot) % 16 || ((((uintptr_t)cache) | ((uintptr_t)qa)) & 15))
+        return TB_ERR_UNSUPPORTED;
     if (tiles == 0) return 0;
     const int hc = H < LM_ROWS ? H : LM_ROWS;
     LatentMmaArgs a{(const __nv_bfloat16*)qa, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial,
@@ -320,8 +332,7 @@ int tb_latent_attention_mma_bf16(const void* qa, const void* q, void* out, float
     else if (nt8 <= 8) rc = latent_mma_go<8>(a, tiles, smem, s);
     else rc = latent_mma_go<16>(a, tiles, smem, s);
     if (rc || splits == 1) return rc;
-    TB_LAUNCH((latent_merge_kernel), (nt * H + 3) / 4, 128, 0, s, (const float*)partial, (__nv_bfloat16*)out, nt * H,
-              splits, rank);
+    TB_LAUNCH((latent_merge_kernel), nt * H, 128, 0, s, (const float*)partial, (__nv_bfloat16*)out, splits, rank);
     return tb_last_error();
 }
 }

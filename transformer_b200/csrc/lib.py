@@ -49,9 +49,13 @@ _SIGNATURES: Dict[str, str] = {
     "tb_gemm_simt_batched_f32": "pppllliiiiiii", "tb_gemm_simt_batched_bf16": "pppllliiiiiii",
     "tb_gemm_skinny_glu_bf16": "pppppliiiiiiiipiiff",
     "tb_gemm_tc_glu_bf16": "ppppiiiiiiiff",
+    "tb_post_add_rmsnorm_router_f32": "pppppipfpfpppppiiiii", "tb_post_add_rmsnorm_router_bf16": "pppppipfpfpppppiiiii",
+    "tb_add_rmsnorm_router_scored_f32": "pppppippfpppppiiii", "tb_add_rmsnorm_router_scored_bf16": "pppppippfpppppiiii",
+    "tb_router_rows_scored_bf16": "pppppppppiiii",
     "tb_router_scored_f32": "pppppppppiiii", "tb_router_scored_bf16": "pppppppppiiii",
     "tb_moe_identity_rows_f32": "pppppiiii", "tb_moe_identity_rows_bf16": "pppppiiii",
     "tb_mlstm_scan_f32": "pppppppiiiiiff", "tb_mlstm_scan_bf16": "pppppppiiiiiff",
+    "tb_mlstm_chunk_f32": "pppppppiiiiiff", "tb_mlstm_chunk_bf16": "pppppppiiiiiff",
     "tb_mlstm_out_f32": "ppippiiif", "tb_mlstm_out_bf16": "ppippiiif",
     "tb_latent_prep_f32": "pippfpppppippiiiii", "tb_latent_prep_bf16": "pippfpppppippiiiii",
     "tb_latent_attention_mma_bf16": "ppppppppppppiiiiiiiiiiif",

@@ -27,12 +27,6 @@ struct DispatchLists {
     unsigned* done;
 };
 
-// How the logits become a choice.  scored == 0: the k largest logits, softmax over the kept (router_pick).
-// scored == 1: softmax over all outputs, the k largest of score + bias, weights = scores (router_pick_scored).
-struct RouterRule {
-    int scored;
-    const float* bias;
-};
 
 template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
@@ -130,7 +124,7 @@ template <int NT, int RR_WARPS>   // tiles of 8 experts; warps that split the wi
 __global__ void __launch_bounds__(RR_WARPS * 32)
 router_rows_kernel(const __nv_bfloat16* __restrict__ x1, const __nv_bfloat16* __restrict__ wr,
                    int* __restrict__ topk_idx, float* __restrict__ topk_w, float* __restrict__ logits_out, int nt, int d,
-                   int E, int k, const DispatchLists lists) {
+                   int E, int k, const DispatchLists lists, const RouterRule rule) {
     constexpr int EP = 8 * NT;
     constexpr int U = NT <= 2 ? 4 : NT == 4 ? 2 : 1;     // chunks of 32 columns in flight per warp
     __shared__ float part[RR_WARPS][RR_ROWS][EP + 1];
@@ -204,7 +198,14 @@ router_rows_kernel(const __nv_bfloat16* __restrict__ x1, const __nv_bfloat16* __
         if (logits_out && row0 + r < nt && e < E) logits_out[(size_t)(row0 + r) * E + e] = v;
     }
     __syncthreads();
-    if (k <= ROUTER_PICK_SERIAL_K && E * k <= 256) {
+    if (rule.scored) {       // a warp per token; the scores go where the second warp's partial sums were
+        for (int r = warp; r < RR_ROWS; r += RR_WARPS) {
+            const int t = row0 + r;
+            if (t < nt)
+                router_pick_scored(&part[0][r][0], &part[1][r][0], rule.bias, topk_idx + (size_t)t * k,
+                                   topk_w + (size_t)t * k, E, k, lane);
+        }
+    } else if (k <= ROUTER_PICK_SERIAL_K && E * k <= 256) {
         const int t = row0 + (int)threadIdx.x;
         if (threadIdx.x < RR_ROWS && t < nt)
             router_pick_serial(&part[0][threadIdx.x][0], topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k);
@@ -402,9 +403,9 @@ int tb_moe_identity_rows_bf16(const void* x1, void* y, const int* group_offsets,
     return identity_rows_launch<__nv_bfloat16>(x1, y, group_offsets, sorted_token, row_group, x_div, M, d, first, s);
 }
 // Router for many tokens (bfloat16, up to 64 experts, a width that is a multiple of 32); `done` as in tb_router_*.
-int tb_router_rows_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out,
-                        int* group_offsets, int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E,
-                        int k, cudaStream_t s) {
+static int router_rows_entry(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out,
+                             int* group_offsets, int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E,
+                             int k, RouterRule rule, cudaStream_t s) {
     if (nt < 0 || d <= 0 || E <= 0 || k <= 0 || k > E) return TB_ERR_ARG;
     if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
     if (E > 64 || d % 32 || (((uintptr_t)x1 | (uintptr_t)wr) & 15)) return TB_ERR_UNSUPPORTED;
@@ -413,11 +414,24 @@ int tb_router_rows_bf16(const void* x1, const void* wr, int* topk_idx, float* to
     const int grid = (nt + RR_ROWS - 1) / RR_ROWS;
     const __nv_bfloat16* x = (const __nv_bfloat16*)x1;
     const __nv_bfloat16* w = (const __nv_bfloat16*)wr;
-    if (E <= 8) TB_LAUNCH((router_rows_kernel<1, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
-    else if (E <= 16) TB_LAUNCH((router_rows_kernel<2, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
-    else if (E <= 32) TB_LAUNCH((router_rows_kernel<4, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
-    else TB_LAUNCH((router_rows_kernel<8, 8>), grid, 256, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists);
+    if (E <= 8) TB_LAUNCH((router_rows_kernel<1, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists, rule);
+    else if (E <= 16) TB_LAUNCH((router_rows_kernel<2, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists, rule);
+    else if (E <= 32) TB_LAUNCH((router_rows_kernel<4, 16>), grid, 512, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists, rule);
+    else TB_LAUNCH((router_rows_kernel<8, 8>), grid, 256, 0, s, x, w, topk_idx, topk_w, logits_out, nt, d, E, k, lists, rule);
     return tb_last_error();
+}
+int tb_router_rows_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, float* logits_out,
+                        int* group_offsets, int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E,
+                        int k, cudaStream_t s) {
+    return router_rows_entry(x1, wr, topk_idx, topk_w, logits_out, group_offsets, sorted_token, pair_row, done, nt, d, E,
+                             k, RouterRule{0, nullptr}, s);
+}
+// The same with the scored rule (see tb_router_scored_*).
+int tb_router_rows_scored_bf16(const void* x1, const void* wr, const float* bias, int* topk_idx, float* topk_w,
+                               int* group_offsets, int* sorted_token, int* pair_row, unsigned* done, int nt, int d,
+                               int E, int k, cudaStream_t s) {
+    return router_rows_entry(x1, wr, topk_idx, topk_w, nullptr, group_offsets, sorted_token, pair_row, done, nt, d, E, k,
+                             RouterRule{1, bias}, s);
 }
 int tb_moe_dispatch(const int* topk_idx, int* group_offsets, int* sorted_token, int* pair_row, int M, int k, int E,
                     cudaStream_t s) {
@@ -441,6 +455,7 @@ int tb_moe_combine_bf16(const void* y, const int* pair_row, const float* topk_w,
 TB_TAPE_REGISTER(tb_router_f32)
 TB_TAPE_REGISTER(tb_router_bf16)
 TB_TAPE_REGISTER(tb_router_rows_bf16)
+TB_TAPE_REGISTER(tb_router_rows_scored_bf16)
 TB_TAPE_REGISTER(tb_router_scored_f32)
 TB_TAPE_REGISTER(tb_router_scored_bf16)
 TB_TAPE_REGISTER(tb_moe_identity_rows_f32)

@@ -89,6 +89,13 @@ __device__ __forceinline__ void router_pick_serial(float* lg, int* __restrict__ 
         if (j < k) w_out[j] = p[j] * inv;
 }
 
+// How the logits become a choice.  scored == 0: the k largest logits, softmax over the kept (router_pick).
+// scored == 1: softmax over all outputs, the k largest of score + bias, weights = scores (router_pick_scored).
+struct RouterRule {
+    int scored;
+    const float* bias;
+};
+
 // Another rule of choice, by one warp:  s = softmax(lg) over ALL E outputs;  the k largest of s + bias are chosen
 // (ties to the lower index; bias may be null);  the weights are the chosen s as they are, not renormalized.
 // lg is consumed, sc [E] is scratch.

@@ -132,6 +132,8 @@ class NormTail:
     k: int = 0
     index: Any = None
     scores: Any = None
+    scored: bool = False     # "router": softmax over all outputs, choice by score + bias, weights = the chosen scores
+    bias: Any = None
 
 
 class Norm(Part):

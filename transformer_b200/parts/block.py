@@ -90,7 +90,8 @@ class SandwichLayer:
     have no feed-forward (then it needs neither "feed_forward_post_norm" nor a feed-forward norm).  The mixer's
     output is handed to the feed-forward's norm as a :class:`NormedDelta`, so its norm, the sum into the stream and
     the next norm are one kernel; the feed-forward's output (the experts' weighted rows, unsummed) is normed and
-    added by the block's last kernel.  The block takes any pending contribution and leaves none."""
+    added by the block's last kernel, or, in a step of one token per sequence, left to the next block's first
+    norm as a :class:`NormedDelta`."""
 
     def __init__(self, spec, dtype, device):
         extra = dict(spec.extra)
@@ -138,11 +139,22 @@ class SandwichLayer:
         pending = self._normed(delta, self.mixer_post_norm)
         if self.feed_forward is not None:
             pending = resolve(pending, self.feed_forward_norm, delta, x=x, ctx=ctx)
-            self.feed_forward_norm.forward(ctx, x, pending, None, x1)
-            lazy = self.feed_forward.forward(ctx, x1, delta)
+            tail = self.feed_forward.norm_tail(ctx, nt)
+            if tail is not None and tail.kind in self.feed_forward_norm.tails:
+                # the feed-forward's router rides along with the kernel that norms the mixer's output, adds it and
+                # norms the sum
+                self.feed_forward_norm.forward(ctx, x, pending, None, x1, tail=tail)
+                lazy = self.feed_forward.forward(ctx, x1, delta, tail=tail)
+            else:
+                self.feed_forward_norm.forward(ctx, x, pending, None, x1)
+                lazy = self.feed_forward.forward(ctx, x1, delta)
             pending = self._normed(delta if lazy is None else lazy, self.feed_forward_post_norm)
-        # the last norm's weight belongs to THIS layer: the sum is done here, so that the layer's launches name no
-        # tensor of another layer (layers of equal parts are replayed with their own tensors put in)
+        if ctx.decode:
+            # one token per sequence: the step is a chain of small kernels, and the last norm, the sum and the next
+            # block's (or the model's last) norm are one of them instead of two
+            return pending
+        # many tokens: the sum is done here, so that the layer's launches name no tensor of another layer (layers of
+        # equal parts are then replayed with their own tensors put in)
         post_add_rmsnorm(ctx.dtype, x, pending, None, None, 0.0, None)
         return None
 

@@ -106,6 +106,11 @@ class MoE(FeedForward):
             # scores over all outputs, choice with the correction, the block that finishes last builds the lists
             done = ctx.scratch("moe.done", (1,), torch.int32, zero=True) if lists is not None else None
             offsets, sorted_token, pair_row = lists if lists is not None else (None, None, None)
+            if self.dtype == torch.bfloat16 and nt > ROUTER_ROWS_FROM and self.R <= 64 and \
+                    lib.try_call("tb_router_rows_scored_bf16", lib.ptr(x1), lib.ptr(self.weights["router"]),
+                                 lib.ptr(self.weights.get("correction")), lib.ptr(idx), lib.ptr(w), lib.ptr(offsets),
+                                 lib.ptr(sorted_token), lib.ptr(pair_row), lib.ptr(done), nt, self.d, self.R, self.k):
+                return idx, w, lists is not None
             lib.call("tb_router_scored_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
                      lib.ptr(self.weights.get("correction")), lib.ptr(idx), lib.ptr(w), lib.ptr(offsets),
                      lib.ptr(sorted_token), lib.ptr(pair_row), lib.ptr(done), nt, self.d, self.R, self.k)
@@ -129,12 +134,13 @@ class MoE(FeedForward):
         return idx, w, fused
 
     def norm_tail(self, ctx, nt):
-        """For a few tokens the router rides along with the norm before this part (the plain rule of choice)."""
-        if nt > ROUTER_TAIL_ROWS or self.scoring != "kept":
+        """For a few tokens the router rides along with the norm before this part."""
+        if nt > ROUTER_TAIL_ROWS:
             return None
         return NormTail("router", weights=self.weights["router"], k=self.k,
                         index=ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32),
-                        scores=ctx.scratch("moe.topk_w", (nt, self.k), torch.float32))
+                        scores=ctx.scratch("moe.topk_w", (nt, self.k), torch.float32),
+                        scored=self.scoring == "all", bias=self.weights.get("correction"))
 
     def forward(self, ctx, x1, out, tail=None) -> None:
         nt = x1.shape[0]

@@ -9,7 +9,8 @@
 
 S, n and m are zero when a sequence starts, are float, and are carried from step to step in the
 engine's per-sequence state (one row per slot); the gates' projections are a float product of their
-own, since their error would add up along the sequence.  The scan is csrc/mlstm.cu.
+own, since their error would add up along the sequence.  The kernels are in csrc/mlstm.cu: token by
+token for decoding, 64 tokens at a time (the recurrence's closed form inside a chunk) for prompts.
 """
 from __future__ import annotations
 
@@ -17,7 +18,10 @@ import torch
 
 from ..csrc import lib
 from .base import MIXERS, Mixer, ParamDecl, StateNeed
-from .linear import SKINNY_MAX_ROWS, gemm_simt, matmul_nt
+from .linear import matmul_nt
+
+
+USE_CHUNKS = True      # prompts: the kernel that takes 64 tokens at a time
 
 
 @MIXERS.register("mlstm")
@@ -57,12 +61,11 @@ class MatrixMemory(Mixer):
         z = ctx.scratch("mlstm.z", (nt, self.z_width), self.dtype)
         matmul_nt(x1, w["wqkvg"], z)
         gates = ctx.scratch("mlstm.gates", (nt, 2 * H), torch.float32)
-        if nt <= SKINNY_MAX_ROWS:
-            matmul_nt(x1, w["wif"], gates)
-        else:       # a handful of columns: the general kernel, float out
-            gemm_simt(x1, w["wif"], gates, out_kind=0 if self.dtype == torch.float32 else 1)
+        matmul_nt(x1, w["wif"], gates)         # float out on both paths
         o = ctx.scratch("mlstm.o", (nt, H * self.vdim), torch.float32)
-        lib.call("tb_mlstm_scan_" + sfx, lib.ptr(z), lib.ptr(gates), lib.ptr(w["bif"]), lib.ptr(state), lib.ptr(o),
+        # prompts: 64 tokens of a sequence side by side; decoding: token by token, the state in registers
+        kernel = "tb_mlstm_scan_" if ctx.decode or not USE_CHUNKS else "tb_mlstm_chunk_"
+        lib.call(kernel + sfx, lib.ptr(z), lib.ptr(gates), lib.ptr(w["bif"]), lib.ptr(state), lib.ptr(o),
                  lib.ptr(ctx.seq_start), lib.ptr(ctx.slots), ctx.B, self.z_width, H, self.dim, self.vdim, self.cap,
                  self.dim ** -0.5)
         y = ctx.scratch("mlstm.y", (nt, H * self.vdim), self.dtype)

@@ -26,9 +26,7 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, x, delta, rows, y, warm=None, tail=None) -> None:
         if isinstance(delta, NormedDelta):
-            if tail is not None:
-                raise ValueError("a norm that is handed a normed delta computes no tail")
-            post_add_rmsnorm(self.dtype, x, delta, rows, self.weights["weight"], self.eps, y)
+            post_add_rmsnorm(self.dtype, x, delta, rows, self.weights["weight"], self.eps, y, tail=tail)
             return
         n_out = y.shape[0]
         wy = idx = wts = None
@@ -40,6 +38,16 @@ class RMSNorm(Norm):
             # widths) gets the norm alone and the router's own kernel
             E = tail.weights.shape[0]
             sfx = lib.suffix(self.dtype)
+            if tail.scored:
+                if lib.try_call("tb_add_rmsnorm_router_scored_" + sfx, lib.ptr(x), lib.ptr(delta), lib.ptr(wy),
+                                lib.ptr(idx), lib.ptr(wts), k, lib.ptr(rows), lib.ptr(self.weights["weight"]), self.eps,
+                                lib.ptr(y), lib.ptr(tail.weights), lib.ptr(tail.bias), lib.ptr(tail.index),
+                                lib.ptr(tail.scores), n_out, self.width, E, tail.k):
+                    return
+                lib.call("tb_add_rmsnorm_" + sfx, lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx), lib.ptr(wts), k,
+                         lib.ptr(rows), lib.ptr(self.weights["weight"]), self.eps, lib.ptr(y), n_out, self.width, 0, 0)
+                _route(sfx, y, tail, n_out, self.width)
+                return
             if lib.try_call("tb_add_rmsnorm_router_" + sfx, lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
                             lib.ptr(wts), k, lib.ptr(rows), lib.ptr(self.weights["weight"]), self.eps, lib.ptr(y),
                             lib.ptr(tail.weights), lib.ptr(tail.index), lib.ptr(tail.scores), n_out, self.width, E,
@@ -56,13 +64,33 @@ class RMSNorm(Norm):
                  self.width, lib.ptr(warm), 0 if warm is None else warm.numel() * warm.element_size())
 
 
-def post_add_rmsnorm(dtype, x, pending: NormedDelta, rows, weight, eps, y) -> None:
+def _route(sfx, y, tail, n_out, width) -> None:
+    """The router of the rows ``y`` by a kernel of its own, into the tail's index and scores."""
+    E = tail.weights.shape[0]
+    if tail.scored:
+        lib.call("tb_router_scored_" + sfx, lib.ptr(y), lib.ptr(tail.weights), lib.ptr(tail.bias), lib.ptr(tail.index),
+                 lib.ptr(tail.scores), 0, 0, 0, 0, n_out, width, E, tail.k)
+    else:
+        lib.call("tb_router_" + sfx, lib.ptr(y), lib.ptr(tail.weights), lib.ptr(tail.index), lib.ptr(tail.scores),
+                 0, 0, 0, 0, 0, n_out, width, E, tail.k)
+
+
+def post_add_rmsnorm(dtype, x, pending: NormedDelta, rows, weight, eps, y, tail=None) -> None:
     """x[rows] += pending.delta / rms(pending.delta) * pending.weight (written back when ``rows`` is None), then
-    y = x / rms(x) * weight; with ``y`` None only the sum."""
+    y = x / rms(x) * weight; with ``y`` None only the sum.  ``tail``: a "router" NormTail computed along the way."""
     delta, wy, idx, wts, k = pending.delta, None, None, None, 0
     if isinstance(delta, WeightedRows):
         wy, idx, wts, k, delta = delta.rows, delta.index, delta.weights, delta.k, None
     n_out = x.shape[0] if y is None else y.shape[0]
-    lib.call("tb_post_add_rmsnorm_" + lib.suffix(dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
+    sfx = lib.suffix(dtype)
+    if tail is not None and rows is None and y is not None:
+        if lib.try_call("tb_post_add_rmsnorm_router_" + sfx, lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
+                        lib.ptr(wts), k, lib.ptr(pending.weight), float(pending.eps), lib.ptr(weight), float(eps),
+                        lib.ptr(y), lib.ptr(tail.weights), lib.ptr(tail.bias), lib.ptr(tail.index), lib.ptr(tail.scores),
+                        n_out, x.shape[1], tail.weights.shape[0], tail.k, 1 if tail.scored else 0):
+            return
+    lib.call("tb_post_add_rmsnorm_" + sfx, lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
              lib.ptr(wts), k, lib.ptr(pending.weight), float(pending.eps), lib.ptr(rows), lib.ptr(weight), float(eps),
              lib.ptr(y), n_out, x.shape[1])
+    if tail is not None:
+        _route(sfx, y, tail, n_out, x.shape[1])

@@ -463,12 +463,12 @@ def test_clamped_gate_in_every_product_kernel(rows):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M", [3, 100])
-def test_products_batched_over_heads_with_pitches(dtype, M):
+@pytest.mark.parametrize("M, K", [(3, 24), (100, 24), (8, 64), (16, 128)])
+def test_products_batched_over_heads_with_pitches(dtype, M, K):
     from transformer_b200.parts.linear import batched_matmul
     g = torch.Generator().manual_seed(M)
     td = torch.float32 if dtype == "float32" else torch.bfloat16
-    H, K, N, pad = 5, 24, 40, 8
+    H, N, pad = 5, 40, 8
     a = torch.randn(M, H, K + pad, generator=g).to(td)
     w = (torch.randn(H, N, K, generator=g) * 0.3).to(td)
     out = torch.zeros(M, H, N, dtype=td, device="cuda")

@@ -16,7 +16,9 @@
 // Sizes: rank a multiple of 32 up to 512, rank + rot a multiple of 16; anything else goes to the general kernel.
 #include "common.cuh"
 
-#define LM_WARPS 4
+// warps per block: 4 (any rank that is a multiple of 32), or 8 when the rank is a multiple of 64: twice the warps
+// on an SM to hide the latencies of a k-step's chain of ldmatrix and mma (with four, no unit was busy for more than
+// a third of the time and an SM held eight warps)
 #define LM_ROWS 16
 #define LM_KEYS TB_PAGE     // keys per tile = one page
 
@@ -59,8 +61,10 @@ __device__ __forceinline__ void lm_cp16(void* dst, const void* src) {
 }
 
 // NT = n8 tiles of the output per warp (rank / 4 / 8, rounded up to the instantiated sizes)
-template <int NT>
+template <int NT, int LM_WARPS>
 __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentMmaArgs a) {
+    constexpr int KPW = LM_KEYS / LM_WARPS;      // keys of a page per warp in the scores' phase: 16 or 8
+    constexpr int RPW = LM_ROWS / LM_WARPS;      // rows per warp in the softmax phase: 4 or 2
     pdl_sync();
     extern __shared__ __align__(16) unsigned char lm_smem[];
     const int DK = a.rank + a.rot;
@@ -122,9 +126,9 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    float mx[4], sum[4];               // of rows 4 warp .. 4 warp + 3 (the same in every lane)
+    float mx[RPW], sum[RPW];           // of rows RPW warp .. (the same in every lane)
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < RPW; ++r) {
         mx[r] = -INFINITY;
         sum[r] = 0.f;
     }
@@ -139,18 +143,65 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
         }
         asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        // ---- 1. scores of this warp's 16 keys ----------------------------------------------------------------
+        // ---- 1. scores of this warp's keys ----------------------------------------------------------------------
+        if constexpr (LM_WARPS == 8) {
+            // 8 keys = one tile of 8 columns; one ldmatrix.x4 of the keys serves two k-steps
+            float sc[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
+            const __nv_bfloat16* qa_p = q_s + (lane & 15) * pitch + (lane >> 4) * 8;
+            const __nv_bfloat16* kb_p = k_s + (warp * 8 + (lane & 7)) * pitch + (lane >> 3) * 8;
+            int k0 = 0;
+#pragma unroll 2
+            for (; k0 + 32 <= DK; k0 += 32) {
+                unsigned af[4], ag[4], bf[4];
+                lm_ldmatrix_x4(bf, kb_p + k0);
+                lm_ldmatrix_x4(af, qa_p + k0);
+                lm_ldmatrix_x4(ag, qa_p + k0 + 16);
+                lm_mma(sc, af, bf[0], bf[1]);
+                lm_mma(sd, ag, bf[2], bf[3]);
+            }
+            if (k0 < DK) {        // 16 entries left: the second half of the keys' fragment lies past them and is not used
+                unsigned af[4], bf[4];
+                lm_ldmatrix_x4(bf, kb_p + k0);
+                lm_ldmatrix_x4(af, qa_p + k0);
+                lm_mma(sc, af, bf[0], bf[1]);
+            }
+            const int c = warp * 8 + 2 * t4;
+            s_s[g * (LM_KEYS + 1) + c] = (sc[0] + sd[0]) * a.scale;
+            s_s[g * (LM_KEYS + 1) + c + 1] = (sc[1] + sd[1]) * a.scale;
+            s_s[(g + 8) * (LM_KEYS + 1) + c] = (sc[2] + sd[2]) * a.scale;
+            s_s[(g + 8) * (LM_KEYS + 1) + c + 1] = (sc[3] + sd[3]) * a.scale;
+        } else
         {
+            // two chains of sums (even and odd k-steps), so that a product does not wait for the one before it, and
+            // the fragments of several k-steps in flight
             float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float sd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
             const __nv_bfloat16* qa_p = q_s + (lane & 15) * pitch + (lane >> 4) * 8;
             const __nv_bfloat16* kb_p = k_s + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * pitch + ((lane >> 3) & 1) * 8;
-            for (int k0 = 0; k0 < DK; k0 += 16) {
+            int k0 = 0;
+#pragma unroll 2
+            for (; k0 + 32 <= DK; k0 += 32) {
+                unsigned af[4], bf[4], ag[4], bg[4];
+                lm_ldmatrix_x4(af, qa_p + k0);
+                lm_ldmatrix_x4(bf, kb_p + k0);
+                lm_ldmatrix_x4(ag, qa_p + k0 + 16);
+                lm_ldmatrix_x4(bg, kb_p + k0 + 16);
+                lm_mma(sc[0], af, bf[0], bf[1]);
+                lm_mma(sc[1], af, bf[2], bf[3]);
+                lm_mma(sd[0], ag, bg[0], bg[1]);
+                lm_mma(sd[1], ag, bg[2], bg[3]);
+            }
+            if (k0 < DK) {
                 unsigned af[4], bf[4];
                 lm_ldmatrix_x4(af, qa_p + k0);
                 lm_ldmatrix_x4(bf, kb_p + k0);
                 lm_mma(sc[0], af, bf[0], bf[1]);
                 lm_mma(sc[1], af, bf[2], bf[3]);
             }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[nt][e] += sd[nt][e];
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 const int c = warp * 16 + nt * 8 + 2 * t4;
@@ -161,10 +212,10 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
             }
         }
         __syncthreads();
-        // ---- 2. softmax of this warp's 4 rows ------------------------------------------------------------------
+        // ---- 2. softmax of this warp's rows --------------------------------------------------------------------
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int row = warp * 4 + r, pos = pos_s[row];
+        for (int r = 0; r < RPW; ++r) {
+            const int row = warp * RPW + r, pos = pos_s[row];
             const int j0 = pg * LM_KEYS + lane, j1 = j0 + 32;
             const bool see0 = pos >= 0 && j0 <= pos && pos - j0 < a.window;
             const bool see1 = pos >= 0 && j1 <= pos && pos - j1 < a.window;
@@ -219,9 +270,9 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
     float* max_s = s_s;             // free by now
     if (lane == 0) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            sum_s[warp * 4 + r] = sum[r];
-            max_s[warp * 4 + r] = mx[r];
+        for (int r = 0; r < RPW; ++r) {
+            sum_s[warp * RPW + r] = sum[r];
+            max_s[warp * RPW + r] = mx[r];
         }
     }
     __syncthreads();
@@ -289,15 +340,15 @@ latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict
     }
 }
 
-template <int NT>
+template <int NT, int W>
 static int latent_mma_go(const LatentMmaArgs& a, int tiles, size_t smem, cudaStream_t s) {
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        tb_note_error(cudaFuncSetAttribute(latent_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024));
+        tb_note_error(cudaFuncSetAttribute(latent_mma_kernel<NT, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024));
         raised = true;
     }
     dim3 grid(tiles, (a.H + a.heads_per_block - 1) / a.heads_per_block, a.splits);
-    TB_LAUNCH((latent_mma_kernel<NT>), grid, LM_WARPS * 32, smem, s, a);
+    TB_LAUNCH((latent_mma_kernel<NT, W>), grid, W * 32, smem, s, a);
     return tb_last_error();
 }
 
@@ -325,12 +376,19 @@ int tb_latent_attention_mma_bf16(const void* qa, const void* q, void* out, float
     const size_t smem = (size_t)(LM_ROWS + LM_KEYS) * pitch * 2 + LM_ROWS * (LM_KEYS + 1) * 4 + LM_ROWS * (LM_KEYS + 8) * 2 +
                         2 * LM_ROWS * 4 + LM_ROWS * 4;
     if (smem > 120 * 1024) return TB_ERR_UNSUPPORTED;
-    const int nt8 = rank / LM_WARPS / 8;
     int rc;
-    if (nt8 <= 2) rc = latent_mma_go<2>(a, tiles, smem, s);
-    else if (nt8 <= 4) rc = latent_mma_go<4>(a, tiles, smem, s);
-    else if (nt8 <= 8) rc = latent_mma_go<8>(a, tiles, smem, s);
-    else rc = latent_mma_go<16>(a, tiles, smem, s);
+    if (rank % 64 == 0) {               // eight warps: rank / 8 columns of the output each
+        const int nt8 = rank / 8 / 8;
+        if (nt8 <= 2) rc = latent_mma_go<2, 8>(a, tiles, smem, s);
+        else if (nt8 <= 4) rc = latent_mma_go<4, 8>(a, tiles, smem, s);
+        else rc = latent_mma_go<8, 8>(a, tiles, smem, s);
+    } else {
+        const int nt8 = rank / 4 / 8;
+        if (nt8 <= 2) rc = latent_mma_go<2, 4>(a, tiles, smem, s);
+        else if (nt8 <= 4) rc = latent_mma_go<4, 4>(a, tiles, smem, s);
+        else if (nt8 <= 8) rc = latent_mma_go<8, 4>(a, tiles, smem, s);
+        else rc = latent_mma_go<16, 4>(a, tiles, smem, s);
+    }
     if (rc || splits == 1) return rc;
     TB_LAUNCH((latent_merge_kernel), nt * H, 128, 0, s, (const float*)partial, (__nv_bfloat16*)out, splits, rank);
     return tb_last_error();

@@ -53,7 +53,14 @@ WIDE = config(128, 128, [
     (memory(2, 32, 64, 10.0), experts(4, 1, 2, 64, 1.0)),
     (latent(8, 16, 32, 16, 64, 32, 100, kv_from=0), experts(4, 0, 1, 64, 1.0)),
 ])
-CONFIGS = {"mixed": (MIXED, 1), "latent": (ONLY_LATENT, 2), "memory": (ONLY_MEMORY, 3), "experts": (ONLY_EXPERTS, 4),
+# sizes that are multiples of nothing: every vectorized or tensor-core form refuses them; the first layer a matrix
+# memory, a window of one token, all experts chosen
+ODD = config(77, 100, [
+    (memory(3, 12, 10, 5.0), experts(3, 0, 3, 20, 0.5)),
+    (latent(5, 12, 6, 10, 20, 14, 1), None),
+    (latent(2, 6, 6, 4, 20, 10, 200, kv_from=1), experts(2, 1, 1, 12, 3.0)),
+], eps=1e-4, scale=0.5)
+CONFIGS = {"odd": (ODD, 6), "mixed": (MIXED, 1), "latent": (ONLY_LATENT, 2), "memory": (ONLY_MEMORY, 3), "experts": (ONLY_EXPERTS, 4),
            "wide": (WIDE, 5)}
 STD = {"wide": 0.08}      # weights' deviation where it is not 0.15: twice the width, half the deviation
 

@@ -156,6 +156,20 @@ def test_sizes_that_reach_the_tensor_core_kernels(dtype, folders):
     T.check_request(cfg, tensors, tokens, rows, routes, dtype, "wide")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sizes_that_no_fast_kernel_takes(dtype, folders):
+    cfg, tensors = SP.read_folder(folders["odd"])
+    tokens = _tokens(folders["odd"], 80, 8)
+    rows, routes = T.run_cuts(_load(folders["odd"], dtype), tokens, [66, 3])
+    T.check_request(cfg, tensors, tokens, rows, routes, dtype, "odd")
+    batch = _load(folders["odd"], dtype)
+    slots = [batch.open() for _ in range(3)]
+    lg = batch.step(slots, [tokens[:5], tokens[:66], tokens[:1]]).cpu()
+    tol = 1e-4 if dtype == "float32" else 2 * T.BF16_REL_TOL * float(lg.abs().max())
+    for i, n in enumerate((5, 66, 1)):
+        assert float((lg[i] - rows[n - 1]).abs().max()) <= tol, f"request {i} in a batch"
+
+
 def test_greedy_generation_through_the_entry_point(folders):
     import transformer_b200 as tb
     cfg, tensors = SP.read_folder(folders["mixed"])
@@ -268,7 +282,8 @@ def _latent_attention(dtype, H, rank, rot, window, lens_before, lens_new, q_of, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H, rank, rot, window", [(2, 32, 8, 64), (5, 24, 16, 65), (20, 64, 0, 300), (1, 130, 6, 1)])
+@pytest.mark.parametrize("H, rank, rot, window", [(2, 32, 8, 64), (5, 24, 16, 65), (20, 64, 0, 300), (1, 130, 6, 1),
+                                                  (2, 256, 16, 50), (1, 512, 64, 20)])
 def test_attention_kernel_one_key_that_stands_out_at_every_edge(dtype, H, rank, rot, window):
     """Every head of every query asks, with a score far above the rest, for ONE key: the oldest inside its window,
     the newest outside it, the one at a page's last row or first row, or one hundreds of tokens back.  A window
@@ -290,7 +305,9 @@ def test_attention_kernel_one_key_that_stands_out_at_every_edge(dtype, H, rank, 
 
 
 @pytest.mark.parametrize("splits", [1, 3, 7])
-@pytest.mark.parametrize("H, rank, rot, window", [(2, 32, 16, 64), (5, 96, 16, 65), (20, 64, 0, 300), (16, 128, 32, 1)])
+@pytest.mark.parametrize("H, rank, rot, window", [(2, 32, 16, 64), (5, 96, 16, 65), (20, 64, 0, 300), (16, 128, 32, 1),
+                                                  (16, 256, 32, 100), (16, 512, 64, 70), (3, 160, 16, 40),
+                                                  (2, 288, 16, 30)])
 def test_tensor_core_attention_kernel_at_every_edge(H, rank, rot, window, splits):
     """The same questions put to the tensor-core kernel, with the key range whole and in slices."""
     def keys(b, n, g):

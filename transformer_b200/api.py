@@ -10,7 +10,7 @@ import torch
 from . import architectures  # noqa: F401  (fills the registry)
 from .config.registry import ConfigError, architecture_for
 from .engine.engine import Engine
-from .weights.loader import load_weights
+from .weights.loader import load_weights, tensor_shapes
 from .weights.random_init import random_device_weights, write_model_folder
 
 _DTYPES = {
@@ -51,6 +51,8 @@ def load(folder: str, dtype="bfloat16", device: Union[str, torch.device] = "cuda
     dt = parse_dtype(dtype)
     dev = torch.device(device)
     arch, meta = _typed(read_config(folder))
+    if arch.refine is not None:
+        meta = arch.refine(meta, tensor_shapes(folder))
     rules = arch.tensor_plan(meta)
     weights = load_weights(folder, rules, dt, dev)
     return Engine(arch.build_spec(meta), weights, dt, dev, max_tokens=max_tokens, max_slots=max_slots,

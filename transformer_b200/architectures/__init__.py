@@ -1,2 +1,2 @@
 """Architectures known to the registry.  Importing this package registers them."""
-from . import llama, salepel  # noqa: F401
+from . import llama, salepel, zufadra  # noqa: F401

@@ -85,22 +85,23 @@ class CacheStorage:
 
 @CACHE_KINDS.register("full")
 class CacheGroup(CacheStorage):
-    """Keys and values of every position, in the pages of the common pool."""
+    """Keys and values of every position, in the pages of the common pool.  ``need.params`` may give ``dv``, the size of
+    a value head where it differs from a key head's (``need.dh``)."""
 
     def __init__(self, need: CacheNeed, runs: List[int], *, n_pages: int, max_slots: int, max_context: int,
                  dtype, device):
         super().__init__(need, runs, n_pages=n_pages, max_slots=max_slots, max_context=max_context, dtype=dtype,
                          device=device)
-        shape = (len(runs), n_pages, need.nkvh, PAGE, need.dh)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        dv = int(need.get().get("dv", need.dh))      # value heads of a size of their own
+        self.k = torch.zeros((len(runs), n_pages, need.nkvh, PAGE, need.dh), dtype=dtype, device=device)
+        self.v = torch.zeros((len(runs), n_pages, need.nkvh, PAGE, dv), dtype=dtype, device=device)
 
     def view(self, index: int, writable: bool) -> CacheView:
         return CacheView(self.k[index], self.v[index], writable=writable, kind=self.need.kind)
 
     @property
     def nbytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 @CACHE_KINDS.register("latent")
@@ -127,9 +128,11 @@ class LatentGroup(CacheStorage):
 class Cache:
     def __init__(self, cache_needs: Sequence[Optional[CacheNeed]], state_needs: Sequence[Optional[StateNeed]],
                  reads_from: Sequence[Optional[int]], *, max_tokens: int, max_context: int,
-                 max_slots: Optional[int], dtype: torch.dtype, device: torch.device):
+                 max_slots: Optional[int], dtype: torch.dtype, device: torch.device,
+                 named_states: Optional[Dict[str, StateNeed]] = None):
         """cache_needs[r] / state_needs[r]: what run r's mixer asks for; reads_from[r]: the run whose
-        cache run r reads instead of owning one."""
+        cache run r reads instead of owning one; named_states: per-sequence state of parts that are not a run's
+        mixer (the embedding), by name."""
         if max_tokens <= 0:
             raise CacheError("max_tokens must be positive")
         n_pages = (max_tokens + PAGE - 1) // PAGE
@@ -166,11 +169,16 @@ class Cache:
         for r, need in enumerate(state_needs):
             if need is not None:
                 self.state[r] = torch.zeros((max_slots, *need.shape), dtype=need.dtype, device=device)
+        self.named: Dict[str, torch.Tensor] = {}
+        for name, need in (named_states or {}).items():
+            self.named[name] = torch.zeros((max_slots, *need.shape), dtype=need.dtype, device=device)
 
     # ---- sequences ------------------------------------------------------------------------
     def open(self) -> int:
         slot = self.table.open()
         for t in self.state.values():
+            t[slot].zero_()
+        for t in self.named.values():
             t[slot].zero_()
         for g in self.groups:
             g.open(slot)
@@ -207,4 +215,5 @@ class Cache:
 
     @property
     def nbytes(self) -> int:
-        return sum(g.nbytes for g in self.groups) + sum(t.numel() * t.element_size() for t in self.state.values())
+        return sum(g.nbytes for g in self.groups) + sum(t.numel() * t.element_size() for t in self.state.values()) + \
+            sum(t.numel() * t.element_size() for t in self.named.values())

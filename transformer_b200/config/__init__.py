@@ -1,4 +1,5 @@
 from .llama import LlamaMeta
 from .salepel import SalepelMeta
+from .zufadra import ZufadraMeta
 from .registry import (Architecture, ConfigError, architecture_for, register_architecture,
                        registered_architectures, unregister_architecture)

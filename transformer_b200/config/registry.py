@@ -7,6 +7,8 @@ An :class:`Architecture` bundles four things and nothing else knows which model 
 * ``tensor_plan(config)``    -- which file tensor (by name) fills which parameter of which part
 * ``names``                  -- the strings ``config.json`` may carry in ``model_type`` / ``architecture`` /
                                 ``architectures`` / ``general.architecture``
+* ``refine(config, shapes)`` -- optional: sizes that only the weight file gives (tensor name -> shape), filled
+                                into the typed configuration before the plan and the spec are made
 
 The reference has no such table: each model is a crate of its own and the only dispatch on the
 architecture string is ``arch == "qwen2"`` (models/llama/common/src/storage.rs:31,45).
@@ -28,6 +30,7 @@ class Architecture:
     build_spec: Callable[[Any], Any]
     tensor_plan: Callable[[Any], Any]
     names: tuple = ()
+    refine: Any = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}

@@ -63,12 +63,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
         ss += v * v;
     }
     ss = block_sum(ss, red);
-    const float rs = 1.0f / sqrtf(ss / (float)d + eps);
+    const float rs = w ? 1.0f / sqrtf(ss / (float)d + eps) : 1.f;      // no weights: the sum itself, rounded to T
     T* yr = y + (size_t)i * d;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float v = xr[c];
         if (has_delta && !write_back) v += delta_at(c);
-        stf(yr + c, v * rs * w[c]);
+        stf(yr + c, w ? v * rs * w[c] : v);
     }
 }
 
@@ -117,7 +117,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
     // this kernel's own weights do not depend on the kernel before it either: they are in registers by the time
     // the wait is over (they are read once per layer and have left L2 since the last step)
     float ww[EARLY ? NORM_CHUNKS : 1][8];
-    if (EARLY) {
+    if (EARLY && w) {
 #pragma unroll
         for (int j = 0; j < NORM_CHUNKS; ++j) {
             const int c = (threadIdx.x + j * NORM_THREADS) * 8;
@@ -203,9 +203,17 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
         }
     }
     if (!y) return;                 // the sum alone
+    T* yr = y + (size_t)i * d;
+    if (!w) {                       // no weights: y is the sum itself, rounded to T (a part that reads the stream as it is)
+#pragma unroll
+        for (int j = 0; j < NORM_CHUNKS; ++j) {
+            const int c = (threadIdx.x + j * NORM_THREADS) * 8;
+            if (c < d) store8(yr + c, v[j]);
+        }
+        return;
+    }
     ss = block_sum(ss, red);
     const float rs = 1.0f / sqrtf(ss / (float)d + eps);
-    T* yr = y + (size_t)i * d;
 #pragma unroll
     for (int j = 0; j < NORM_CHUNKS; ++j) {
         const int c = (threadIdx.x + j * NORM_THREADS) * 8;
@@ -320,9 +328,13 @@ post_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, cons
         ss2 += v * v;
     }
     if (!y) return;
+    T* yr = y + (size_t)i * d;
+    if (!w) {                       // no weights: the sum itself, rounded to T (each thread wrote these entries itself)
+        for (int c = threadIdx.x; c < d; c += blockDim.x) stf(yr + c, row[c]);
+        return;
+    }
     ss2 = block_sum(ss2, red);
     const float rs2 = 1.0f / sqrtf(ss2 / (float)d + eps);
-    T* yr = y + (size_t)i * d;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         stf(yr + c, row[c] * rs2 * w[c]);
         if (tail.w) row[c] = ldf(yr + c);       // what the router reads: the row as stored
@@ -347,6 +359,59 @@ post_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, cons
         else
             router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
     }
+}
+
+// x[i, :] = table[tok_i, :] * scale + pairs[row_i, :], where row_i is a hash of the token and the one before it in
+// its sequence:  (prev * mul_prev + tok * mul_cur) mod buckets;  a sequence's first token takes row `buckets` (the
+// table's last).  The token before a step's first one is per-sequence state (last_token [slots]); the thread
+// block of a sequence's first token of the step reads it and then leaves the sequence's last token of the step there.
+template <typename T>
+__global__ void embed_bigram_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_seq,
+                                    const int* __restrict__ tok_pos, const int* __restrict__ seq_start,
+                                    const int* __restrict__ slots, int* __restrict__ last_token,
+                                    const T* __restrict__ table, const T* __restrict__ pairs, float* __restrict__ x,
+                                    int d, float scale, int buckets, int mul_prev, int mul_cur) {
+    pdl_sync();
+    __shared__ int prev_s;
+    const int i = blockIdx.x;
+    const int tok = tokens[i];
+    if (threadIdx.x == 0) {
+        const int b = tok_seq[i];
+        int prev;
+        if (i == seq_start[b]) {
+            int* keep = last_token + slots[b];
+            prev = *keep;
+            *keep = tokens[seq_start[b + 1] - 1];
+        } else {
+            prev = tokens[i - 1];
+        }
+        prev_s = prev;
+    }
+    __syncthreads();
+    const int r = tok_pos[i] == 0 ? buckets
+                                  : (int)(((long long)prev_s * mul_prev + (long long)tok * mul_cur) % (long long)buckets);
+    const T* src = table + (size_t)tok * d;
+    const T* add = pairs + (size_t)r * d;
+    float* dst = x + (size_t)i * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) dst[c] = ldf(src + c) * scale + ldf(add + c);
+}
+
+template <typename T>
+static int embed_bigram_launch(const int* tokens, const int* tok_seq, const int* tok_pos, const int* seq_start,
+                               const int* slots, int* last_token, const void* table, const void* pairs, float* x,
+                               int nt, int d, float scale, int buckets, int mul_prev, int mul_cur, cudaStream_t s) {
+    if (nt < 0 || d <= 0 || buckets <= 0 || mul_prev < 0 || mul_cur < 0 || !last_token) return TB_ERR_ARG;
+    if (nt == 0) return 0;
+    TB_LAUNCH((embed_bigram_kernel<T>), nt, d >= 1024 ? 256 : 128, 0, s, tokens, tok_seq, tok_pos, seq_start, slots,
+              last_token, (const T*)table, (const T*)pairs, x, d, scale, buckets, mul_prev, mul_cur);
+    return tb_last_error();
+}
+
+// v[i] *= scale over n floats (logits with a fixed multiplier)
+__global__ void scale_f32_kernel(float* __restrict__ v, long long n, float scale) {
+    pdl_sync();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        v[i] *= scale;
 }
 
 template <typename T>
@@ -404,7 +469,7 @@ static int post_add_rmsnorm_launch(float* x, const void* delta, const void* wy, 
                                    const float* w, float eps, void* y, int n_out, int d, cudaStream_t s,
                                    RouterTail<T> tail = RouterTail<T>{nullptr, 0, 0, nullptr, nullptr,
                                                                       RouterRule{0, nullptr}}) {
-    if (n_out < 0 || d <= 0 || !post_w || (y && !w)) return TB_ERR_ARG;
+    if (n_out < 0 || d <= 0 || !post_w || (tail.w && !w)) return TB_ERR_ARG;
     if ((delta == nullptr) == (wy == nullptr)) return TB_ERR_ARG;
     if (wy && (!pair_row || !topk_w || k <= 0)) return TB_ERR_ARG;
     if (tail.w && (!y || tail.E <= 0 || tail.k <= 0 || tail.k > tail.E || !tail.idx || !tail.wts)) return TB_ERR_ARG;
@@ -423,6 +488,22 @@ static int post_add_rmsnorm_launch(float* x, const void* delta, const void* wy, 
 }
 
 extern "C" {
+#define TB_EMBED_BIGRAM(NAME, T)                                                                                      \
+    int NAME(const int* tokens, const int* tok_seq, const int* tok_pos, const int* seq_start, const int* slots,       \
+             int* last_token, const void* table, const void* pairs, float* x, int nt, int d, float scale,             \
+             int buckets, int mul_prev, int mul_cur, cudaStream_t s) {                                                \
+        return embed_bigram_launch<T>(tokens, tok_seq, tok_pos, seq_start, slots, last_token, table, pairs, x, nt, d, \
+                                      scale, buckets, mul_prev, mul_cur, s);                                          \
+    }
+TB_EMBED_BIGRAM(tb_embed_bigram_f32, float)
+TB_EMBED_BIGRAM(tb_embed_bigram_bf16, __nv_bfloat16)
+int tb_scale_f32(float* v, long long n, float scale, cudaStream_t s) {
+    if (n < 0) return TB_ERR_ARG;
+    if (n == 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    TB_LAUNCH(scale_f32_kernel, (int)(blocks > 4096 ? 4096 : blocks), 256, 0, s, v, n, scale);
+    return tb_last_error();
+}
 int tb_embed_f32(const int* tokens, const void* table, float* x, int nt, int d, cudaStream_t s) {
     return embed_launch<float>(tokens, table, x, nt, d, 1.0f, s);
 }
@@ -533,3 +614,6 @@ TB_TAPE_REGISTER(tb_add_rmsnorm_router_f32)
 TB_TAPE_REGISTER(tb_add_rmsnorm_router_bf16)
 TB_TAPE_REGISTER(tb_add_rmsnorm_router_scored_f32)
 TB_TAPE_REGISTER(tb_add_rmsnorm_router_scored_bf16)
+TB_TAPE_REGISTER(tb_embed_bigram_f32)
+TB_TAPE_REGISTER(tb_embed_bigram_bf16)
+TB_TAPE_REGISTER(tb_scale_f32)

@@ -60,13 +60,22 @@ _SIGNATURES: Dict[str, str] = {
     "tb_latent_prep_f32": "pippfpppppippiiiii", "tb_latent_prep_bf16": "pippfpppppippiiiii",
     "tb_latent_attention_mma_bf16": "ppppppppppppiiiiiiiiiiif",
     "tb_latent_attention_f32": "pppppppppppiiiiiiiiiif", "tb_latent_attention_bf16": "pppppppppppiiiiiiiiiif",
+    "tb_embed_bigram_f32": "pppppppppiifiii", "tb_embed_bigram_bf16": "pppppppppiifiii",
+    "tb_scale_f32": "plf",
+    "tb_qknorm_rope_cache_f32": "pippfpppippppiiiiiii", "tb_qknorm_rope_cache_bf16": "pippfpppippppiiiiiii",
+    "tb_attention_window_f32": "pppppppppppiiiiiiiiiiiiff", "tb_attention_window_bf16": "pppppppppppiiiiiiiiiiiiff",
+    "tb_delta_prep_f32": "pipppppppppppppiiiiiiii",
+    "tb_delta_prep_bf16": "pipppppppppppppiiiiiiii",
+    "tb_delta_scan": "ppppppppiiiiii",
+    "tb_bias_glu_f32": "pppii", "tb_bias_glu_bf16": "pppii",
+    "tb_add_bias_f32": "ppii", "tb_add_bias_bf16": "ppii",
 }
 class TapeArg(ctypes.Union):
     _fields_ = [("p", ctypes.c_void_p), ("i", ctypes.c_int), ("f", ctypes.c_float), ("l", ctypes.c_longlong),
                 ("u", ctypes.c_ulonglong)]
 
 
-TAPE_MAX_ARGS = 24
+TAPE_MAX_ARGS = 28
 
 
 class TapeEntry(ctypes.Structure):
@@ -80,7 +89,7 @@ class TapeMap(ctypes.Structure):
     _fields_ = [("base", ctypes.c_ulonglong), ("size", ctypes.c_ulonglong), ("delta", ctypes.c_longlong)]
 
 
-_NO_STREAM = {"tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
+_NO_STREAM = {"tb_delta_state_size": "iiiii", "tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
               "tb_attention_tc_tile_tokens": ""}
 
 _lock = threading.Lock()
@@ -366,6 +375,12 @@ def raise_for_status(code: int, recover=None) -> None:
 def mlstm_state_size(dim: int, vdim: int) -> int:
     """Floats of state that the matrix-memory kernel keeps per (sequence, head)."""
     return library().tb_mlstm_state_size(dim, vdim)
+
+
+def delta_state_size(kv_heads: int, heads: int, dim: int, vdim: int, taps: int) -> int:
+    """Floats of state that the delta-rule kernels keep per sequence (the heads' memories, then the convolution's
+    last inputs)."""
+    return library().tb_delta_state_size(kv_heads, heads, dim, vdim, taps)
 
 
 def latent_attention_tile_tokens(heads: int) -> int:

@@ -176,6 +176,103 @@ static int rope_cache_launch(void* qkv, const int* tok_seq, const int* tok_pos, 
     return tb_last_error();
 }
 
+// The same step for a mixer that norms its whole query and key projections first and rotates only a part of every
+// head, with value heads of a size of their own.  Row of z: q (nh dk) | k (nkvh dk) | v (nkvh dv) | ...
+//   q <- q / sqrt(mean over ALL nh dk entries (q^2) + eps) * q_norm,   k alike over its nkvh dk entries;
+//   the first rdims entries of every head turn by the token's angles (table [positions, rdims / 2]), the rest pass;
+//   q is written back in place, k and v go to the cache:  K [pages, nkvh, TB_PAGE, dk],  V [pages, nkvh, TB_PAGE, dv].
+// Statistics, the norm and the rotation are float; one rounding at each store.  A block per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qknorm_rope_cache_kernel(T* __restrict__ z, int ldz, const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                         float eps, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                         const int* __restrict__ page_table, int max_pages, const float* __restrict__ cos_t,
+                         const float* __restrict__ sin_t, T* __restrict__ kc, T* __restrict__ vc, int nh, int nkvh,
+                         int dk, int dv, int rdims, int half_pairing) {
+    pdl_sync();
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int nq = nh * dk, nk = nkvh * dk;
+    T* row = z + (size_t)t * ldz;
+    float rq = 1.f, rk = 1.f;
+    if (q_norm) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < nq; c += blockDim.x) {
+            const float x = ldf(row + c);
+            ss += x * x;
+        }
+        rq = 1.0f / sqrtf(block_sum(ss, red) / (float)nq + eps);
+    }
+    if (k_norm) {
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+            const float x = ldf(row + nq + c);
+            ss += x * x;
+        }
+        rk = 1.0f / sqrtf(block_sum(ss, red) / (float)nk + eps);
+    }
+    const int rp = rdims >> 1;                  // rotated pairs per head
+    const float* cs = cos_t + (size_t)pos * rp;
+    const float* sn = sin_t + (size_t)pos * rp;
+    size_t cache_row = 0;
+    if (kc) {
+        const int page = page_table[(size_t)tok_seq[t] * max_pages + pos / TB_PAGE];
+        cache_row = (size_t)page * nkvh * TB_PAGE + (pos % TB_PAGE);      // + head * TB_PAGE, times the head size
+    }
+    // rotated pairs of the query heads, then of the key heads
+    for (int idx = threadIdx.x; idx < (nh + nkvh) * rp; idx += blockDim.x) {
+        const int head = idx / rp, i = idx - head * rp;
+        const int i0 = half_pairing ? i : 2 * i, i1 = half_pairing ? i + rp : 2 * i + 1;
+        const bool is_q = head < nh;
+        const int base = head * dk;             // column of the head's first entry in the row (q and k are adjacent)
+        const float* w = is_q ? q_norm : k_norm;
+        const int wb = is_q ? base : base - nq;
+        const float r = is_q ? rq : rk;
+        const float x0 = ldf(row + base + i0) * r * (w ? w[wb + i0] : 1.f);
+        const float x1 = ldf(row + base + i1) * r * (w ? w[wb + i1] : 1.f);
+        const float c = cs[i], s = sn[i];
+        const float y0 = x0 * c - x1 * s, y1 = x1 * c + x0 * s;
+        if (is_q) {
+            stf(row + base + i0, y0);
+            stf(row + base + i1, y1);
+        } else if (kc) {
+            T* dst = kc + (cache_row + (size_t)(head - nh) * TB_PAGE) * dk;
+            stf(dst + i0, y0);
+            stf(dst + i1, y1);
+        }
+    }
+    // the entries that pass
+    const int rest = dk - rdims;
+    for (int idx = threadIdx.x; idx < (nh + nkvh) * rest; idx += blockDim.x) {
+        const int head = idx / rest, c = rdims + idx - head * rest;
+        const bool is_q = head < nh;
+        const int base = head * dk;
+        const float* w = is_q ? q_norm : k_norm;
+        const float y = ldf(row + base + c) * (is_q ? rq : rk) * (w ? w[(is_q ? base : base - nq) + c] : 1.f);
+        if (is_q) stf(row + base + c, y);
+        else if (kc) stf(kc + (cache_row + (size_t)(head - nh) * TB_PAGE) * dk + c, y);
+    }
+    if (vc)
+        for (int idx = threadIdx.x; idx < nkvh * dv; idx += blockDim.x) {
+            const int head = idx / dv, c = idx - head * dv;
+            vc[(cache_row + (size_t)head * TB_PAGE) * dv + c] = row[nq + nk + idx];
+        }
+}
+
+template <typename T>
+static int qknorm_rope_cache_launch(void* z, int ldz, const float* q_norm, const float* k_norm, float eps,
+                                    const int* tok_seq, const int* tok_pos, const int* page_table, int max_pages,
+                                    const float* cos_t, const float* sin_t, void* kc, void* vc, int nt, int nh,
+                                    int nkvh, int dk, int dv, int rdims, int half_pairing, cudaStream_t s) {
+    if (nt < 0 || nh <= 0 || nkvh <= 0 || dk <= 0 || dv <= 0 || rdims < 0 || rdims > dk || (rdims & 1)) return TB_ERR_ARG;
+    if ((kc == nullptr) != (vc == nullptr) || ldz < (nh + nkvh) * dk + nkvh * dv) return TB_ERR_ARG;
+    if (nt == 0) return 0;
+    TB_LAUNCH((qknorm_rope_cache_kernel<T>), nt, 256, 0, s, (T*)z, ldz, q_norm, k_norm, eps, tok_seq, tok_pos, page_table,
+              max_pages, cos_t, sin_t, (T*)kc, (T*)vc, nh, nkvh, dk, dv, rdims, half_pairing);
+    return tb_last_error();
+}
+
 extern "C" {
 int tb_rope_cache_f32(void* qkv, const int* tok_seq, const int* tok_pos, const int* page_table, int max_pages,
                       const float* cos_t, const float* sin_t, void* kc, void* vc, int nt, int nh, int nkvh,
@@ -189,9 +286,21 @@ int tb_rope_cache_bf16(void* qkv, const int* tok_seq, const int* tok_pos, const 
     return rope_cache_launch<__nv_bfloat16>(qkv, tok_seq, tok_pos, page_table, max_pages, cos_t, sin_t, kc, vc,
                                             nt, nh, nkvh, dh, half_pairing, s);
 }
+#define TB_QKNORM_ROPE(NAME, T)                                                                                        \
+    int NAME(void* z, int ldz, const float* q_norm, const float* k_norm, float eps, const int* tok_seq,               \
+             const int* tok_pos, const int* page_table, int max_pages, const float* cos_t, const float* sin_t,        \
+             void* kc, void* vc, int nt, int nh, int nkvh, int dk, int dv, int rdims, int half_pairing,               \
+             cudaStream_t s) {                                                                                        \
+        return qknorm_rope_cache_launch<T>(z, ldz, q_norm, k_norm, eps, tok_seq, tok_pos, page_table, max_pages,      \
+                                           cos_t, sin_t, kc, vc, nt, nh, nkvh, dk, dv, rdims, half_pairing, s);       \
+    }
+TB_QKNORM_ROPE(tb_qknorm_rope_cache_f32, float)
+TB_QKNORM_ROPE(tb_qknorm_rope_cache_bf16, __nv_bfloat16)
 }
 
 // replayable from C++ (tape.h)
 #include "tape.h"
 TB_TAPE_REGISTER(tb_rope_cache_f32)
 TB_TAPE_REGISTER(tb_rope_cache_bf16)
+TB_TAPE_REGISTER(tb_qknorm_rope_cache_f32)
+TB_TAPE_REGISTER(tb_qknorm_rope_cache_bf16)

@@ -16,7 +16,7 @@
 #include <tuple>
 #include <utility>
 
-#define TB_TAPE_MAX_ARGS 24
+#define TB_TAPE_MAX_ARGS 28
 
 union TapeArg {
     const void* p;

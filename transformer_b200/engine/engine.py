@@ -66,7 +66,9 @@ class Engine:
         mixers = [self.layers[e.layer].mixer for e in runs]
         self.cache = Cache([m.cache_need() for m in mixers], [m.state_need() for m in mixers],
                            [e.cache_of for e in runs], max_tokens=max_tokens, max_context=spec.max_context,
-                           max_slots=max_slots, dtype=dtype, device=device)
+                           max_slots=max_slots, dtype=dtype, device=device,
+                           named_states={"embedding": self.embed.state_need()} if self.embed.state_need() else None)
+        self._embed_state = self.cache.named.get("embedding")
         # weak: the workspace must not keep its owner alive (see weak_callback); an engine that goes out of scope
         # is freed at once, by reference count, and its CUDA graphs with it
         self.workspace = Workspace(device, on_grow=weak_callback(self._drop_graphs))
@@ -334,7 +336,10 @@ class Engine:
     def _forward_on_stream(self, ctx: StepContext, logits_out=None) -> torch.Tensor:
         nt, d, V = ctx.nt, self.spec.width, self.spec.vocab
         x = ctx.scratch("stream", (nt, d), torch.float32)
-        self.embed.forward(ctx, x)
+        if self._embed_state is not None:
+            self.embed.forward(ctx, x, state=self._embed_state)     # an embedding that carries something per sequence
+        else:
+            self.embed.forward(ctx, x)
         pending = None
         taping = self.use_tapes and self.recorder is None
         tapes = {}                  # kind of run and of what it is handed -> (recorded run, its tape)

@@ -3,4 +3,4 @@ of a block, each behind a registry."""
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, CacheNeed, Embedding,
                    FeedForward, Head, Mixer, Norm, NormedDelta, ParamDecl, Part, Position, StateNeed, WeightedRows)
 from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry
-from . import attention, block, ends, feed_forward, latent_attention, mlstm, norm, rope  # noqa: F401  (registers the built-in kinds)
+from . import attention, block, channel_delta, ends, feed_forward, latent_attention, mlstm, norm, rope  # noqa: F401  (registers the built-in kinds)

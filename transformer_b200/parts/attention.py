@@ -3,6 +3,16 @@
 qkv = x1 Wqkv^T (one merged product, heads ordered q, k, v); rotary encoding of q and k fused with
 the write of k and v into the cache; causal attention of the step's tokens over everything their
 sequences hold; out = o Wo^T.  The residual sum is the caller's (the block's) business.
+
+Further mechanisms, each a parameter of the same mixer (a model that names none of them runs exactly the path
+above): value heads of a size of their own (``dv``); a score multiplier other than dh^-1/2 (``scale``); capped
+scores, cap * tanh(score / cap) (``softcap``); a sliding window (``window``: position i sees j iff i - j < window)
+that keeps the sequence's first tokens visible (``keep_first``), the cache keeping every position; an RMS norm over
+the WHOLE query projection and the whole key projection before the rotation (``qk_norm="whole"``, weights
+``q_norm`` / ``k_norm``, ``eps``); a rotation of only the first entries of every head (the rotary part's ``dh``
+below the head's); a gate on the output, o * sigmoid(Wg x1), whose projection rides in the merged product
+(``gate``).  With any of them the step runs  merged product -> norm + rotation + cache write (one kernel) ->
+windowed attention with the gate in its epilogue -> output product  (csrc/attention_window.cu, rope_cache.cu).
 """
 from __future__ import annotations
 
@@ -24,7 +34,8 @@ RING_BLOCKS_PER_SM = 2  # decoding: the keys are sliced until that kernel has th
 
 @MIXERS.register("attention")
 class Attention(Mixer):
-    """params: width, nh, nkvh, dh, position (a PartSpec of a rotary encoding, or None)."""
+    """params: width, nh, nkvh, dh, position (a PartSpec of a rotary encoding, or None); optional: dv, scale, softcap,
+    window, keep_first, qk_norm, eps, gate (see the head of this file)."""
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -34,12 +45,35 @@ class Attention(Mixer):
         self.dh = int(params["dh"])
         if self.nh % self.nkvh:
             raise ValueError(f"{self.nh} heads cannot share {self.nkvh} key/value heads")
-        if self.dh % 16 or self.dh > 256:
-            raise ValueError(f"the attention kernels take head sizes 16, 32, ..., 256; got {self.dh}")
+        if self.dh <= 0 or self.dh > 256:
+            raise ValueError(f"the attention kernels take head sizes up to 256; got {self.dh}")
         pos = params.get("position")
         self.position = POSITIONS.build(pos, dtype, device) if isinstance(pos, PartSpec) else None
-        self.qkv_width = (self.nh + 2 * self.nkvh) * self.dh
-        self.scale = 1.0 / math.sqrt(self.dh)
+        self.dv = int(params.get("dv") or self.dh)
+        self.softcap = float(params.get("softcap") or 0.0)
+        self.window = int(params.get("window") or 0)            # 0: no window
+        self.keep_first = int(params.get("keep_first") or 0)
+        self.qk_norm = params.get("qk_norm")
+        self.gate = bool(params.get("gate", False))
+        self.eps = float(params.get("eps", 0.0))
+        if self.qk_norm not in (None, "whole"):
+            raise ValueError(f"unknown query/key norm {self.qk_norm!r}")
+        if self.dv <= 0 or self.dv > 256 or self.window < 0 or self.keep_first < 0 or self.softcap < 0:
+            raise ValueError("value heads of 1..256 entries; window, keep_first and softcap not negative")
+        # any of the further mechanisms takes the step to the windowed kernels
+        self.extended = bool(self.dv != self.dh or self.softcap or self.window or self.qk_norm or self.gate or
+                             "scale" in params)
+        if not self.extended and (self.dh % 16):
+            raise ValueError(f"the attention kernels take head sizes 16, 32, ..., 256; got {self.dh}")
+        self.rdims = 0
+        if self.extended and self.position is not None:
+            if device.type == "cuda" and self.position.rotation() is None:
+                raise ValueError("the windowed attention takes a rotary position encoding or none")
+            self.rdims = int(pos.get()["dh"])
+            if self.rdims > self.dh:
+                raise ValueError(f"a rotation of {self.rdims} entries does not fit heads of {self.dh}")
+        self.qkv_width = (self.nh + self.nkvh) * self.dh + self.nkvh * self.dv + (self.nh * self.dv if self.gate else 0)
+        self.scale = float(params["scale"]) if "scale" in params else 1.0 / math.sqrt(self.dh)
         # query tiles this mixer asks the step to plan: the general kernel's, and the prompt kernel's
         self.general_tile = lib.attention_tile_tokens(self.nh, self.nkvh)
         # bfloat16 prompts: the mma.sync kernel takes every head size, the tcgen05 kernel heads of 64 and 128
@@ -58,8 +92,11 @@ class Attention(Mixer):
     def parameters(self):
         decl = {
             "wqkv": ParamDecl((self.qkv_width, self.d)),
-            "wo": ParamDecl((self.d, self.nh * self.dh)),
+            "wo": ParamDecl((self.d, self.nh * self.dv)),
         }
+        if self.qk_norm:
+            decl["q_norm"] = ParamDecl((self.nh * self.dh,), "norm", "ones")
+            decl["k_norm"] = ParamDecl((self.nkvh * self.dh,), "norm", "ones")
         if self.position is not None:      # what the position encoding has learned travels with its mixer
             decl.update({"position." + n: d for n, d in self.position.parameters().items()})
         return decl
@@ -70,9 +107,37 @@ class Attention(Mixer):
             self.position.bind({n: tensors["position." + n] for n in self.position.parameters()})
 
     def cache_need(self):
+        if self.dv != self.dh:
+            return CacheNeed("full", self.nkvh, self.dh, (("dv", self.dv),))
         return CacheNeed("full", self.nkvh, self.dh)
 
+    def _forward_window(self, ctx, x1, out, cache) -> None:
+        """The step with the further mechanisms: see the head of this file."""
+        nt = x1.shape[0]
+        sfx = lib.suffix(self.dtype)
+        w = self.weights
+        z = ctx.scratch("attn.qkv", (nt, self.qkv_width), self.dtype)        # q | k | v | gate
+        matmul_nt(x1, w["wqkv"], z)
+        table = ctx.page_table(cache)
+        cos = sin = None
+        half = 0
+        if self.rdims:
+            cos, sin, half = self.position.rotation()
+        kc, vc = (cache.k, cache.v) if cache.writable else (None, None)
+        lib.call("tb_qknorm_rope_cache_" + sfx, lib.ptr(z), self.qkv_width, lib.ptr(w.get("q_norm")),
+                 lib.ptr(w.get("k_norm")), self.eps, lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table),
+                 ctx.max_pages, lib.ptr(cos), lib.ptr(sin), lib.ptr(kc), lib.ptr(vc), nt, self.nh, self.nkvh, self.dh,
+                 self.dv, self.rdims, half)
+        o = ctx.scratch("attn.o", (nt, self.nh * self.dv), self.dtype)
+        gate = z[:, (self.nh + self.nkvh) * self.dh + self.nkvh * self.dv:] if self.gate else None
+        window = self.window if self.window else 1 << 30
+        run_window_attention(ctx, self, z, o, gate, cache, table, nt, window)
+        matmul_nt(o, w["wo"], out)
+
     def forward(self, ctx, x1, out, cache, state) -> None:
+        if self.extended:
+            self._forward_window(ctx, x1, out, cache)
+            return
         nt = x1.shape[0]
         sfx = lib.suffix(self.dtype)
         qkv = ctx.scratch("attn.qkv", (nt, self.qkv_width), self.dtype)
@@ -172,3 +237,18 @@ class Attention(Mixer):
         return lib.try_call("tb_attention_decode_" + sfx, lib.ptr(qkv), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                             lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(partial), nt,
                             ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, self.scale)
+
+
+def run_window_attention(ctx, m, z, o, gate, cache, table, nt, window) -> None:
+    """The windowed attention of the step's rotated queries ``z`` over the cache, into ``o`` (gate applied)."""
+    sfx = lib.suffix(m.dtype)
+    tiles = ctx.tiles(m.general_tile)
+    # slices of the visited keys so that a few sequences still fill the GPU: a function of the batch's shape alone (a
+    # captured graph keeps it), and no more than the window has 32-key tiles
+    splits = ctx.attention_splits(tiles.count, m.nh, m.nkvh)
+    splits = int(max(1, min(splits, (min(window, 1 << 20) + m.keep_first + 31) // 32 + 1)))
+    partial = ctx.scratch("attn.partial", (nt, m.nh, splits, m.dv + 2), torch.float32) if splits > 1 else None
+    lib.call("tb_attention_window_" + sfx, lib.ptr(z), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v), lib.ptr(gate),
+             lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos), lib.ptr(table),
+             lib.ptr(partial), tiles.count, nt, ctx.max_pages, m.qkv_width, m.qkv_width, m.nh, m.nkvh, m.dh, m.dv,
+             splits, window, m.keep_first, m.scale, m.softcap)

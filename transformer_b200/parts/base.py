@@ -8,7 +8,8 @@ talks to parts only through the methods below.
 kind          interface
 ============  ===================================================================================
 Embedding     ``forward(ctx, x)``: fill the float residual stream ``x`` [nt, d] for the step's tokens
-              (``ctx.tok_ids``, and ``ctx.tok_pos`` for an encoding that adds positions here).
+              (``ctx.tok_ids``, and ``ctx.tok_pos`` for an encoding that adds positions here).  With a
+              ``state_need()`` it is handed its per-sequence state as ``state=``.
 Norm          ``forward(ctx, x, delta, rows, y)``: ``v = x[rows] + delta[rows]`` (float sum; written
               back to ``x`` when ``rows`` is None), ``y = norm(v)``.  ``x`` is the float residual
               stream, ``delta`` the previous part's output or None.
@@ -182,6 +183,12 @@ class Position(Part):
 
 
 class Embedding(Part):
+    def state_need(self) -> Optional[StateNeed]:
+        """A tensor of fixed size per sequence that the embedding carries from step to step (the token before, for
+        an embedding of token pairs), or None.  An embedding that asks for one is called as
+        ``forward(ctx, x, state=)`` with the tensor [slots, *shape]; rows are addressed by ``ctx.slots``."""
+        return None
+
     def forward(self, ctx, x) -> None:
         raise NotImplementedError
 

@@ -20,8 +20,9 @@ ROUTER_TAIL_ROWS = 256      # up to this many tokens the norm before the experts
 
 @FEED_FORWARDS.register("swiglu")
 class DenseSwiGLU(FeedForward):
-    """params: width, di.  gate_up = x1 Wgu^T (gate rows first), h = silu(gate) * up, out = h Wd^T
-    (compute.rs:278-292)."""
+    """params: width, di, bias (default False).  gate_up = x1 Wgu^T (gate rows first), h = silu(gate) * up,
+    out = h Wd^T (compute.rs:278-292).  With ``bias`` all three projections have one: ``bgu`` (gate's, then up's)
+    and ``bd``, float."""
     graph_safe = True
     launches_only = True
 
@@ -29,13 +30,26 @@ class DenseSwiGLU(FeedForward):
         super().__init__(params, dtype, device)
         self.d = int(params["width"])
         self.di = int(params["di"])
+        self.bias = bool(params.get("bias", False))
 
     def parameters(self):
-        return {"wgu": ParamDecl((2 * self.di, self.d)), "wd": ParamDecl((self.d, self.di))}
+        decl = {"wgu": ParamDecl((2 * self.di, self.d)), "wd": ParamDecl((self.d, self.di))}
+        if self.bias:
+            decl["bgu"] = ParamDecl((2 * self.di,), "norm", "normal")
+            decl["bd"] = ParamDecl((self.d,), "norm", "normal")
+        return decl
 
     def forward(self, ctx, x1, out) -> None:
         nt = x1.shape[0]
         h = ctx.scratch("ff.h", (nt, self.di), self.dtype)
+        if self.bias:
+            sfx = lib.suffix(self.dtype)
+            gu = ctx.scratch("ff.gu", (nt, 2 * self.di), self.dtype)
+            matmul_nt(x1, self.weights["wgu"], gu)
+            lib.call("tb_bias_glu_" + sfx, lib.ptr(gu), lib.ptr(self.weights["bgu"]), lib.ptr(h), nt, self.di)
+            matmul_nt(h, self.weights["wd"], out)
+            lib.call("tb_add_bias_" + sfx, lib.ptr(out), lib.ptr(self.weights["bd"]), nt, self.d)
+            return
         grouped_matmul(x1, self.weights["wgu"], h, swiglu=True)
         matmul_nt(h, self.weights["wd"], out)
 

@@ -7,7 +7,8 @@ from .base import NORMS, Norm, NormedDelta, ParamDecl, WeightedRows
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """params: width, eps.  Statistics and the residual sum are float; one rounding at the store."""
+    """params: width, eps, mult (default 1).  y = v / rms(v) * weight * mult.  Statistics and the residual sum are
+    float; one rounding at the store.  The multiplier is folded into the bound weight (a float product, once)."""
 
     graph_safe = True
     launches_only = True
@@ -20,9 +21,15 @@ class RMSNorm(Norm):
         super().__init__(params, dtype, device)
         self.width = int(params["width"])
         self.eps = float(params["eps"])
+        self.mult = float(params.get("mult", 1.0))
 
     def parameters(self):
         return {"weight": ParamDecl((self.width,), "norm", "ones")}
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if self.mult != 1.0:
+            self.weights["weight"] = self.weights["weight"].float() * self.mult
 
     def forward(self, ctx, x, delta, rows, y, warm=None, tail=None) -> None:
         if isinstance(delta, NormedDelta):
@@ -62,6 +69,32 @@ class RMSNorm(Norm):
         lib.call("tb_add_rmsnorm_" + lib.suffix(self.dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
                  lib.ptr(wts), k, lib.ptr(rows), lib.ptr(self.weights["weight"]), self.eps, lib.ptr(y), n_out,
                  self.width, lib.ptr(warm), 0 if warm is None else warm.numel() * warm.element_size())
+
+
+@NORMS.register("none")
+class NoNorm(Norm):
+    """params: width.  No norm at all, for blocks whose parts read the residual stream as it is: the pending
+    contribution joins the stream (float sum; a :class:`NormedDelta` is normed on the way) and y is the sum, rounded
+    once to the activation type.  The same kernels as the norm's, without weights."""
+    graph_safe = True
+    launches_only = True
+    takes_weighted_rows = True
+    takes_normed_delta = True
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.width = int(params["width"])
+
+    def forward(self, ctx, x, delta, rows, y) -> None:
+        if isinstance(delta, NormedDelta):
+            post_add_rmsnorm(self.dtype, x, delta, rows, None, 0.0, y)
+            return
+        wy = idx = wts = None
+        k = 0
+        if isinstance(delta, WeightedRows):
+            wy, idx, wts, k, delta = delta.rows, delta.index, delta.weights, delta.k, None
+        lib.call("tb_add_rmsnorm_" + lib.suffix(self.dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
+                 lib.ptr(wts), k, lib.ptr(rows), 0, 0.0, lib.ptr(y), y.shape[0], self.width, 0, 0)
 
 
 def _route(sfx, y, tail, n_out, width) -> None:

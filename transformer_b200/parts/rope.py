@@ -17,7 +17,11 @@ _TABLES = {}
 
 @POSITIONS.register("rope")
 class Rope(Position):
-    """params: dh, theta, pairing ("adjacent" | "half"), positions (table length)."""
+    """params: dh, theta, pairing ("adjacent" | "half"), positions (table length), scaling (optional).
+
+    ``scaling`` = (factor, low, high, original) rescales the frequencies by wavelength l = 2 pi / f against a context
+    of ``original`` tokens: f stays where l < original / high, becomes f / factor where l > original / low, and
+    between the two is (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
     graph_safe = True
     launches_only = True
 
@@ -27,6 +31,10 @@ class Rope(Position):
         self.theta = float(params["theta"])
         self.pairing = params.get("pairing", "adjacent")
         self.positions = int(params["positions"])
+        sc = params.get("scaling")
+        self.scaling = None if sc is None else tuple(float(v) for v in sc)
+        if self.scaling is not None and len(self.scaling) != 4:
+            raise ValueError(f"rope scaling is (factor, low, high, original), got {sc!r}")
         if self.dh % 2:
             raise ValueError(f"rotary pairs need an even head size, got {self.dh}")
         if self.pairing not in ("adjacent", "half"):
@@ -41,10 +49,15 @@ class Rope(Position):
         return cos, sin, self.half_pairing
 
     def tables(self):
-        key = (self.dh, self.theta, self.positions, str(self.device))
+        key = (self.dh, self.theta, self.positions, self.scaling, str(self.device))
         if key not in _TABLES:
             i = torch.arange(self.dh // 2, dtype=torch.float64)
             inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.dh)
+            if self.scaling is not None:
+                factor, low, high, original = self.scaling
+                turns = original * inv_freq / (2.0 * torch.pi)          # original / wavelength
+                blend = ((turns - low) / (high - low)).clamp(0.0, 1.0)  # 0: long waves (scaled), 1: short (kept)
+                inv_freq = (1.0 - blend) * inv_freq / factor + blend * inv_freq
             ang = torch.arange(self.positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
             _TABLES[key] = (torch.cos(ang).float().contiguous().to(self.device),
                             torch.sin(ang).float().contiguous().to(self.device))

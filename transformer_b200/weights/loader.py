@@ -130,6 +130,12 @@ def open_tensors(path: str):
     return _Files(path)
 
 
+def tensor_shapes(path: str) -> Dict[str, Tuple[int, ...]]:
+    """{tensor name: shape} of a model's weight file(s), without reading any data."""
+    files = open_tensors(path)
+    return {n: tuple(files.shape_dtype(n)[0]) for n in files.names()}
+
+
 def load_weights(path: str, rules: Sequence[TensorRule], compute_dtype: torch.dtype,
                  device: torch.device) -> Dict[Dest, torch.Tensor]:
     """Read, check, convert and upload.  Returns {dest: device tensor}; a rule without a source in

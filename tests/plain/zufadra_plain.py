@@ -113,10 +113,21 @@ def visible(i: int, j: int, window: int, keep_first: int) -> bool:
     return j <= i and (i - j < window or j < keep_first)
 
 
+def _mask(m: dict, n: int):
+    """(window, keep_first); a mixer without a mask sees every earlier token."""
+    mask = m.get("mask")
+    return (n + 1, 0) if mask is None else (mask["size"], mask.get("keep_first", 0))
+
+
+def cap_scores(s: torch.Tensor, m: dict) -> torch.Tensor:
+    cap = m.get("softcap")
+    return s if not cap else float(cap) * torch.tanh(s / float(cap))
+
+
 def attention_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float, store=None) -> torch.Tensor:
     n = h.shape[0]
     H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    rot, mask = m["rot"], m["mask"]
+    rot, (window, keep_first) = m["rot"], _mask(m, n)
     freqs = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
     q = _keep(h @ w["q"].T, store)
     k = _keep(h @ w["k"].T, store)
@@ -128,14 +139,12 @@ def attention_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: f
     q = _keep(torch.stack([rotate_pairs(q[t], t, freqs) for t in range(n)]), store)
     k = _keep(torch.stack([rotate_pairs(k[t], t, freqs) for t in range(n)]), store)
     out = torch.zeros(n, H, vdim, dtype=h.dtype)
-    cap = float(m["softcap"])
     for t in range(n):
-        js = [j for j in range(t + 1) if visible(t, j, mask["size"], mask["keep_first"])]
+        js = [j for j in range(t + 1) if visible(t, j, window, keep_first)]
         for hd in range(H):
             g = hd // (H // G)
             s = torch.stack([(q[t, hd] * k[j, g]).sum() for j in js]) * m["scale"]
-            s = cap * torch.tanh(s / cap)
-            p = torch.softmax(s, dim=0)
+            p = torch.softmax(cap_scores(s, m), dim=0)
             out[t, hd] = sum(p[a] * v[j, g] for a, j in enumerate(js))
     o = out.reshape(n, H * vdim) * torch.sigmoid(gate)
     return _keep(_keep(o, store) @ w["o"].T, store)
@@ -145,7 +154,7 @@ def attention_mixer_fast(h, w, m, eps, store=None):
     """The same as :func:`attention_mixer` with the scores of all pairs at once (for long sequences)."""
     n = h.shape[0]
     H, G, dim, vdim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    rot, mask = m["rot"], m["mask"]
+    rot, (window, keep_first) = m["rot"], _mask(m, n)
     freqs = torch.tensor(rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling")), dtype=torch.float64)
     q = _keep(h @ w["q"].T, store)
     k = _keep(h @ w["k"].T, store)
@@ -166,14 +175,12 @@ def attention_mixer_fast(h, w, m, eps, store=None):
     q, k = _keep(turn(q), store), _keep(turn(k), store)
     i = torch.arange(n)[:, None]
     j = torch.arange(n)[None, :]
-    see = (j <= i) & ((i - j < mask["size"]) | (j < mask["keep_first"]))
-    cap = float(m["softcap"])
+    see = (j <= i) & ((i - j < window) | (j < keep_first))
     out = torch.zeros(n, H, vdim, dtype=h.dtype)
     for hd in range(H):
         g = hd // (H // G)
         sc = (q[:, hd] @ k[:, g].T) * m["scale"]
-        sc = cap * torch.tanh(sc / cap)
-        sc = sc.masked_fill(~see, float("-inf"))
+        sc = cap_scores(sc, m).masked_fill(~see, float("-inf"))
         out[:, hd] = torch.softmax(sc, dim=-1) @ v[:, g]
     o = out.reshape(n, H * vdim) * torch.sigmoid(gate)
     return _keep(_keep(o, store) @ w["o"].T, store)
@@ -212,7 +219,7 @@ def channel_delta_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, ep
     a = _keep(h @ w["a1"].T, store) @ w["a2"].T + w["dt_bias"]               # [n, H * dim]
     rate = torch.exp(w["A_log"])                                             # [H]
     g = torch.exp(-rate[None, :, None] * torch.nn.functional.softplus(a.view(n, H, dim)))
-    gate = torch.sigmoid(_keep(h @ w["g1"].T, store) @ w["g2"].T).view(n, H, vdim)
+    gate = torch.sigmoid(_keep(_keep(h @ w["g1"].T, store) @ w["g2"].T, store)).view(n, H, vdim)
     out = torch.zeros(n, H, vdim, dtype=h.dtype)
     for hd in range(H):
         kv = hd // (H // G)
@@ -230,8 +237,8 @@ def channel_delta_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, ep
 # feed-forward
 # ----------------------------------------------------------------------------------------------
 def dense_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], store=None) -> torch.Tensor:
-    a = silu(h @ w["gate"].T + w["gate.b"]) * (h @ w["up"].T + w["up.b"])
-    return _keep(_keep(a, store) @ w["down"].T + w["down.b"], store)
+    a = silu(_keep(h @ w["gate"].T, store) + w["gate.b"]) * (_keep(h @ w["up"].T, store) + w["up.b"])
+    return _keep(_keep(_keep(a, store) @ w["down"].T, store) + w["down.b"], store)
 
 
 # ----------------------------------------------------------------------------------------------

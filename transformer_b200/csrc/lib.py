@@ -64,6 +64,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_scale_f32": "plf",
     "tb_qknorm_rope_cache_f32": "pippfpppippppiiiiiii", "tb_qknorm_rope_cache_bf16": "pippfpppippppiiiiiii",
     "tb_attention_window_f32": "pppppppppppiiiiiiiiiiiiff", "tb_attention_window_bf16": "pppppppppppiiiiiiiiiiiiff",
+    "tb_attention_window_mma_bf16": "pppppppppppiiiiiiiiiiiiff",
     "tb_delta_prep_f32": "pipppppppppppppiiiiiiii",
     "tb_delta_prep_bf16": "pipppppppppppppiiiiiiii",
     "tb_delta_scan": "ppppppppiiiiii",
@@ -89,7 +90,7 @@ class TapeMap(ctypes.Structure):
     _fields_ = [("base", ctypes.c_ulonglong), ("size", ctypes.c_ulonglong), ("delta", ctypes.c_longlong)]
 
 
-_NO_STREAM = {"tb_delta_state_size": "iiiii", "tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
+_NO_STREAM = {"tb_attention_window_mma_tile_tokens": "ii", "tb_delta_state_size": "iiiii", "tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
               "tb_attention_tc_tile_tokens": ""}
 
 _lock = threading.Lock()
@@ -381,6 +382,11 @@ def delta_state_size(kv_heads: int, heads: int, dim: int, vdim: int, taps: int) 
     """Floats of state that the delta-rule kernels keep per sequence (the heads' memories, then the convolution's
     last inputs)."""
     return library().tb_delta_state_size(kv_heads, heads, dim, vdim, taps)
+
+
+def attention_window_mma_tile_tokens(nh: int, nkvh: int) -> int:
+    """Query tokens per block of the tensor-core windowed attention (0: it does not take such head groups)."""
+    return library().tb_attention_window_mma_tile_tokens(nh, nkvh)
 
 
 def latent_attention_tile_tokens(heads: int) -> int:

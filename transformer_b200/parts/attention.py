@@ -30,6 +30,7 @@ USE_TCGEN05 = True     # prompts: the tcgen05 kernel before the mma.sync one
 USE_DECODE_RING = True  # decoding: the kernel with a ring of cache pages (TMA, tensor cores) before the register-staged one
 FUSE_DECODE_ROPE = True # decoding: that kernel also rotates q and k and writes the cache (no rotary kernel)
 RING_BLOCKS_PER_SM = 2  # decoding: the keys are sliced until that kernel has this many blocks per SM
+USE_WINDOW_MMA = True   # the windowed path, bfloat16: the tensor-core kernel before the general one
 
 
 @MIXERS.register("attention")
@@ -79,7 +80,12 @@ class Attention(Mixer):
         # bfloat16 prompts: the mma.sync kernel takes every head size, the tcgen05 kernel heads of 64 and 128
         self.prompt_tile = lib.attention_prefill_tile_tokens() if dtype == torch.bfloat16 else 0
         self.tc_tile = lib.attention_tc_tile_tokens() if (self.prompt_tile and self.dh in (64, 128)) else 0
-        self.tile_sizes = [t for t in (self.general_tile, self.prompt_tile, self.tc_tile) if t]
+        # the windowed path on the tensor cores: a block takes all query heads of a key head, 64 rows in all
+        self.window_tile = lib.attention_window_mma_tile_tokens(self.nh, self.nkvh) \
+            if (self.extended and dtype == torch.bfloat16) else 0
+        if self.extended:
+            self.prompt_tile = self.tc_tile = 0
+        self.tile_sizes = [t for t in (self.general_tile, self.prompt_tile, self.tc_tile, self.window_tile) if t]
 
     @property
     def graph_safe(self) -> bool:
@@ -242,6 +248,18 @@ class Attention(Mixer):
 def run_window_attention(ctx, m, z, o, gate, cache, table, nt, window) -> None:
     """The windowed attention of the step's rotated queries ``z`` over the cache, into ``o`` (gate applied)."""
     sfx = lib.suffix(m.dtype)
+    if m.window_tile and USE_WINDOW_MMA:
+        # bfloat16: the tensor-core kernel, for prompts and decoding alike.  Slices of the visited pages so that a few
+        # sequences still fill the GPU: a function of the batch's shape alone (a captured graph keeps it)
+        tiles = ctx.tiles(m.window_tile)
+        pages = (min(window, ctx.engine.spec.max_context) + m.keep_first + 63) // 64 + 2
+        splits = int(max(1, min(16, pages, (2 * ctx.engine.sm_count) // max(1, tiles.count * m.nkvh))))
+        partial = ctx.scratch("attn.partial", (nt, m.nh, splits, m.dv + 2), torch.float32) if splits > 1 else None
+        if lib.try_call("tb_attention_window_mma_bf16", lib.ptr(z), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
+                        lib.ptr(gate), lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos),
+                        lib.ptr(table), lib.ptr(partial), tiles.count, nt, ctx.max_pages, m.qkv_width, m.qkv_width,
+                        m.nh, m.nkvh, m.dh, m.dv, splits, window, m.keep_first, m.scale, m.softcap):
+            return
     tiles = ctx.tiles(m.general_tile)
     # slices of the visited keys so that a few sequences still fill the GPU: a function of the batch's shape alone (a
     # captured graph keeps it), and no more than the window has 32-key tiles

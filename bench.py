@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --design salepel [--sizes s,m]      another design beside Llama-MoE at equal sizes (see bench_design)
+    python bench.py --design zufadra [--sizes s,m]      the Zufadra design beside a dense Llama at equal sizes
 
 The default run has the layer sizes of the LLaMA-MoE-3.5B (4/16) shape (32 layers, width 4096,
 32/32 heads of 128, 16 experts top-4 of width 688, vocabulary 32000, context 4096) with random
@@ -171,9 +172,33 @@ def design_shapes(size):
     return salepel, llama
 
 
+def zufadra_shapes(size):
+    """(Zufadra config, dense Llama config of equal width, depth, heads and feed-forward) for a named size.  Layers
+    alternate between the delta rule and the windowed attention, each followed by the dense feed-forward."""
+    d, L, H, G, dim, window, rank, ff = {
+        "s": (1024, 8, 8, 2, 128, 1024, 64, 2816),
+        "m": (2048, 8, 16, 4, 128, 2048, 128, 5632),
+    }[size]
+    att = {"heads": H, "kv_heads": G, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+           "mask": {"size": window, "keep_first": 4},
+           "rot": {"base": 1000000.0, "dims": dim // 2,
+                   "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    mem = {"heads": H, "kv_heads": H, "dim": dim, "vdim": dim, "conv": 4, "decay_rank": rank, "gate_rank": rank}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = [{"type": "channel_delta" if i % 2 == 0 else "attention", "mixer": mem if i % 2 == 0 else att, "mlp": mlp}
+              for i in range(L)]
+    zufadra = {"architecture": "Zufadra", "vocab": 32000, "width": d, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+               "logit_scale": 0.25, "embedding": {"scale": 12.0, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+               "max_context": 8192, "layers": layers}
+    llama = {"model_type": "llama", "num_hidden_layers": L, "hidden_size": d, "num_attention_heads": H,
+             "num_key_value_heads": G, "head_dim": dim, "intermediate_size": ff, "max_position_embeddings": 8192,
+             "vocab_size": 32000, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "tie_word_embeddings": False}
+    return zufadra, llama
+
+
 def bench_design(args):
-    """Prefill and decode throughput of the Salepel design beside a Llama-MoE of equal sizes, and the device time of
-    every kernel family in one eager step of each (CUDA events around each launch).  One JSON line."""
+    """Prefill and decode throughput of another design beside the closest existing model of equal sizes, and the
+    device time of every kernel family in one eager step of each (CUDA events around each launch).  One JSON line."""
     import torch
     import transformer_b200 as tb
     from transformer_b200.csrc import lib
@@ -182,13 +207,15 @@ def bench_design(args):
     pk = peaks()
     T, B, ctx0, K, W = args.prefill_tokens, args.batch, 1024, args.steps, max(3, args.warmup)
     gen = torch.Generator().manual_seed(7)
-    out = {"metric": "prefill and decode tok/s, Salepel beside Llama-MoE at equal sizes", "unit": "tokens/s",
+    names, shapes = {"salepel": (("salepel", "llama_moe"), design_shapes),
+                     "zufadra": (("zufadra", "llama_dense"), zufadra_shapes)}[args.design]
+    out = {"metric": f"prefill and decode tok/s, {names[0]} beside {names[1]} at equal sizes", "unit": "tokens/s",
            "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic: random weights, random token ids",
            "peaks": pk, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx0, "steps": K, "warmup": W,
            "sizes": {}}
     for size in args.sizes.split(","):
         row = {}
-        for name, cfg in zip(("salepel", "llama_moe"), design_shapes(size)):
+        for name, cfg in zip(names, shapes(size)):
             room = max(T, B * (ctx0 + K * 8 + W + 80)) + 4096
             engine = tb.random_model(cfg, seed=0, dtype=args.dtype, max_tokens=room, max_slots=B + 2,
                                      max_step_tokens=max(8192, T))
@@ -277,7 +304,7 @@ def main():
                     help="layer sizes: the benchmark's (default) or another shape BASELINE.json names")
     ap.add_argument("--prompt-max", type=int, default=0, help="longest prompt drawn (default: the shape's own)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
-    ap.add_argument("--design", default=None, choices=["salepel"],
+    ap.add_argument("--design", default=None, choices=["salepel", "zufadra"],
                     help="instead of the default workload: this design beside the closest existing model at equal "
                          "sizes (prefill of --prefill-tokens, decode at --batch; sizes from --sizes)")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of the named sizes (s, m)")

@@ -391,15 +391,23 @@ def test_delta_rule_kernel_keeps_a_token_for_hundreds_of_steps(G, H, dim, vdim):
     I = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
 
     def run(qkv, decay, beta):
+        # the records the scan reads, per (token, head): q | k | decay (rows padded: 0, 0, 1) | beta, k.q, 0, 0; and v
         n = qkv.shape[0]
-        kq = torch.stack([(qkv[:, (h // (H // G)) * dim:(h // (H // G) + 1) * dim] *
-                           qkv[:, G * dim + (h // (H // G)) * dim:G * dim + (h // (H // G) + 1) * dim]).sum(1)
-                          for h in range(H)], dim=1).contiguous()
+        PER, VP = lib.delta_record_size(dim), lib.delta_value_pitch(vdim)
+        DP = (PER - 4) // 3
+        rec, vals = torch.zeros(n, H, PER), torch.zeros(n, H, VP)
+        rec[:, :, 2 * DP:3 * DP] = 1.0
+        for h in range(H):
+            kv = h // (H // G)
+            q, k = qkv[:, kv * dim:(kv + 1) * dim], qkv[:, G * dim + kv * dim:G * dim + (kv + 1) * dim]
+            rec[:, h, :dim], rec[:, h, DP:DP + dim] = q, k
+            rec[:, h, 2 * DP:2 * DP + dim] = decay[:, h * dim:(h + 1) * dim]
+            rec[:, h, 3 * DP], rec[:, h, 3 * DP + 1] = beta[:, h], (q * k).sum(1)
+            vals[:, h, :vdim] = qkv[:, 2 * G * dim + h * vdim:2 * G * dim + (h + 1) * vdim]
         out = torch.empty(n, H * vdim, device="cuda")
-        d = [t.float().contiguous().cuda() for t in (qkv, decay, beta, kq)]
         # device copies stay in names until the kernel has run: a temporary's memory would be handed to the next one
-        starts, slots = I([0, n]), I([slot])
-        lib.call("tb_delta_scan", lib.ptr(d[0]), lib.ptr(d[1]), lib.ptr(d[2]), lib.ptr(d[3]), lib.ptr(state), lib.ptr(out),
+        d_rec, d_vals, starts, slots = rec.cuda(), vals.cuda(), I([0, n]), I([slot])
+        lib.call("tb_delta_scan", lib.ptr(d_rec), lib.ptr(d_vals), lib.ptr(state), lib.ptr(out),
                  lib.ptr(starts), lib.ptr(slots), 1, G, H, dim, vdim, taps)
         torch.cuda.synchronize()
         return out.cpu()

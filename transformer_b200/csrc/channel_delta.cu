@@ -14,16 +14,25 @@
 // State of one slot (floats): S [H][dim][vdim], then the convolution's inputs [taps - 1][C], C = 2 G dim + H vdim.
 //
 // The scan reads o_t = (gS)^T q + u (k . q) from the SAME pass over the state that gives (gS)^T k, so a token costs
-// one pass for the two sums, a reduction over the four lanes that share a column, and one pass for the update.
-// Work split of the scan: a block = one sequence x one head x 32 columns of the state; a column belongs to four
-// adjacent lanes, which split the rows (chunks of four rows, interleaved), RPT rows each in registers.
+// one pass for the two sums, a reduction over the lanes that share a column, and one pass for the update.
+// Work split of the scan: a block = one sequence x one head x 8 to 32 columns of the state; a column belongs to
+// four to sixteen adjacent lanes, which split the rows (chunks of four rows, interleaved), RPT rows each in
+// registers.  The first kernel leaves one contiguous record per (token, head), so the scan's staging is a plain
+// 16-byte copy.
 #include "common.cuh"
+#include "attention_prefill.cuh"        // cp_async16, cp_async_commit, cp_async_wait
 
 #define CD_UNIT_EPS 1e-6f
-#define CD_SPLIT 4
-#define CD_COLS 32
-#define CD_THREADS (CD_SPLIT * CD_COLS)
+#define CD_THREADS 128
 #define CD_MAX_TAPS 16
+#define CD_TOK 4            // tokens staged in shared memory per barrier
+
+// Rows that the scan's lanes cover for heads of `dim` key channels (dim rounded up to what its forms take), and the
+// lanes that share a column.  A record of one (token, head) for the scan:  q [DP] | k [DP] | g [DP] | beta, k.q, 0, 0
+// (rows beyond dim: q = k = 0, g = 1), then separately v [VP] with VP = vdim rounded up to 32.
+__host__ __device__ inline int cd_rows(int dim) { return dim <= 16 ? 16 : dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : 256; }
+__host__ __device__ inline int cd_record(int dim) { return 3 * cd_rows(dim) + 4; }
+__host__ __device__ inline int cd_vpitch(int vdim) { return (vdim + 31) / 32 * 32; }
 
 struct DeltaPrepArgs {
     const void* z;          // [nt, ldz]: q (G dim) | k (G dim) | v (H vdim) | whatever else the product made
@@ -33,10 +42,8 @@ struct DeltaPrepArgs {
     const float* dt_bias;   // [H dim]
     const float* A_log;     // [H]
     const float* bz;        // [nt, H]      pre-activation of beta
-    float* qkv;             // out [nt, C]
-    float* decay;           // out [nt, H dim]
-    float* beta;            // out [nt, H]
-    float* kq;              // out [nt, H]  k . q of the head's key head (after the unit norms and the scale)
+    float* rec;             // out [nt, H, cd_record(dim)]
+    float* vbuf;            // out [nt, H, cd_vpitch(vdim)]
     const int* tok_seq;
     const int* seq_start;
     const int* slots;
@@ -46,17 +53,23 @@ struct DeltaPrepArgs {
 
 __device__ __forceinline__ float cd_softplus(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
+// A block = one token x one key head g: the convolutions of that head's query and key channels and of the value
+// channels of the heads that read it, the two unit norms, and those heads' decays and betas.
 template <typename T>
-__global__ void __launch_bounds__(256) delta_prep_kernel(const DeltaPrepArgs p) {
+__global__ void __launch_bounds__(128) delta_prep_kernel(const DeltaPrepArgs p) {
     pdl_sync();
-    extern __shared__ float y[];        // [C] the convolution's outputs after silu
-    const int t = blockIdx.x;
+    extern __shared__ float y[];        // [2 dim + per vdim] the convolution's outputs after silu: q, k, v of the group
+    const int t = blockIdx.x, g = blockIdx.y;
     const int b = p.tok_seq[t];
     const int li = t - p.seq_start[b];                  // index of the token among its sequence's tokens of the step
-    const int C = 2 * p.G * p.dim + p.H * p.vdim, taps = p.taps;
+    const int dim = p.dim, vdim = p.vdim, gd = p.G * dim, per = p.H / p.G, taps = p.taps;
+    const int C = 2 * gd + p.H * vdim, n_loc = 2 * dim + per * vdim;
+    const int DP = cd_rows(dim), PER = cd_record(dim), VP = cd_vpitch(vdim);
     const T* z = static_cast<const T*>(p.z);
     float* cs = p.state + (size_t)p.slots[b] * p.state_stride + p.conv_offset;     // [taps - 1][C]
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int i = threadIdx.x; i < n_loc; i += blockDim.x) {
+        // local entry i -> channel c of the row
+        const int c = i < dim ? g * dim + i : i < 2 * dim ? gd + g * dim + (i - dim) : 2 * gd + g * per * vdim + (i - 2 * dim);
         float acc = 0.f, old[CD_MAX_TAPS];
         for (int j = 0; j < taps; ++j) {
             const int back = taps - 1 - j, s = li - back;
@@ -64,17 +77,16 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(const DeltaPrepArgs p) 
             old[j] = x;
             acc += p.wconv[(size_t)c * taps + j] * x;
         }
-        y[c] = acc / (1.0f + expf(-acc));
+        y[i] = acc / (1.0f + expf(-acc));
         if (p.update_state)         // a step of one token per sequence: this thread alone touches its channel's state
             for (int r = 0; r + 1 < taps; ++r) cs[(size_t)r * C + c] = old[r + 1];
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const int dim = p.dim, gd = p.G * p.dim;
-    float* out = p.qkv + (size_t)t * C;
-    for (int g = warp; g < p.G; g += nw) {
-        const float* q = y + g * dim;
-        const float* k = y + gd + g * dim;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* rec = p.rec + ((size_t)t * p.H + (size_t)g * per) * PER;          // the group's first head
+    if (warp == 0) {
+        const float* q = y;
+        const float* k = y + dim;
         float sq = 0.f, sk = 0.f, dot = 0.f;
         for (int c = lane; c < dim; c += 32) {
             sq += q[c] * q[c];
@@ -85,23 +97,34 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(const DeltaPrepArgs p) 
         sk = warp_sum(sk);
         dot = warp_sum(dot);
         const float iq = rsqrtf((float)dim) / sqrtf(sq + CD_UNIT_EPS), ik = 1.0f / sqrtf(sk + CD_UNIT_EPS);
-        for (int c = lane; c < dim; c += 32) {
-            out[g * dim + c] = q[c] * iq;
-            out[gd + g * dim + c] = k[c] * ik;
+        for (int h = 0; h < per; ++h) {
+            float* r = rec + (size_t)h * PER;
+            for (int c = lane; c < DP; c += 32) {
+                r[c] = c < dim ? q[c] * iq : 0.f;
+                r[DP + c] = c < dim ? k[c] * ik : 0.f;
+            }
+            if (lane < 4) {
+                const int hh = g * per + h;
+                r[3 * DP + lane] = lane == 0 ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + hh])) : lane == 1 ? dot * iq * ik : 0.f;
+            }
         }
-        const int per = p.H / p.G;
-        if (lane < per) p.kq[(size_t)t * p.H + g * per + lane] = dot * iq * ik;
-        for (int h = lane + 32; h < per; h += 32) p.kq[(size_t)t * p.H + g * per + h] = dot * iq * ik;
+    } else {
+        const int nth = blockDim.x - 32, id = threadIdx.x - 32;
+        float* vb = p.vbuf + ((size_t)t * p.H + (size_t)g * per) * VP;
+        for (int i = id; i < per * VP; i += nth) {
+            const int h = i / VP, c = i - h * VP;
+            vb[i] = c < vdim ? y[2 * dim + h * vdim + c] : 0.f;
+        }
+        for (int i = id; i < per * DP; i += nth) {
+            const int h = i / DP, c = i - h * DP;
+            float gval = 1.f;
+            if (c < dim) {
+                const int hd = (g * per + h) * dim + c;     // (head, key channel)
+                gval = expf(-expf(p.A_log[hd / dim]) * cd_softplus(p.a[(size_t)t * p.H * dim + hd] + p.dt_bias[hd]));
+            }
+            rec[(size_t)h * PER + 2 * DP + c] = gval;
+        }
     }
-    for (int c = 2 * gd + threadIdx.x; c < C; c += blockDim.x) out[c] = y[c];
-    for (int i = threadIdx.x; i < p.H * dim; i += blockDim.x) {
-        const int h = i / dim;
-        p.decay[(size_t)t * p.H * dim + i] =
-            expf(-expf(p.A_log[h]) * cd_softplus(p.a[(size_t)t * p.H * dim + i] + p.dt_bias[i]));
-    }
-    if (threadIdx.x < p.H) p.beta[(size_t)t * p.H + threadIdx.x] = 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + threadIdx.x]));
-    for (int h = threadIdx.x + blockDim.x; h < p.H; h += blockDim.x)
-        p.beta[(size_t)t * p.H + h] = 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + h]));
 }
 
 // After a step that brought a sequence more than one token: the last taps - 1 inputs of every channel, from the
@@ -125,10 +148,8 @@ __global__ void __launch_bounds__(256) delta_conv_state_kernel(const DeltaPrepAr
 }
 
 struct DeltaScanArgs {
-    const float* qkv;       // [nt, C]
-    const float* decay;     // [nt, H dim]
-    const float* beta;      // [nt, H]
-    const float* kq;        // [nt, H]
+    const float* rec;       // [nt, H, cd_record(dim)]
+    const float* vbuf;      // [nt, H, cd_vpitch(vdim)]
     float* state;           // [slots, state_stride], S first
     float* out;             // [nt, H vdim]
     const int* seq_start;
@@ -137,85 +158,85 @@ struct DeltaScanArgs {
     int G, H, dim, vdim;
 };
 
-template <int RPT>
+// RPT rows of a column per thread, SPLIT lanes per column: SPLIT * RPT = cd_rows(dim), CD_THREADS / SPLIT columns a
+// block.  The records of four tokens at a time are copied to shared memory by cp.async while the four before them
+// are computed; one barrier per four tokens.
+template <int RPT, int SPLIT>
 __global__ void __launch_bounds__(CD_THREADS) delta_scan_kernel(const DeltaScanArgs a) {
     pdl_sync();
-    constexpr int DP = RPT * CD_SPLIT;                  // rows the block's lanes cover (dim rounded up)
-    constexpr int NF = (3 * DP + CD_THREADS - 1) / CD_THREADS;
-    __shared__ __align__(16) float sm[2][3][DP];        // [parity][q | k | g][row]
+    constexpr int DP = RPT * SPLIT;
+    constexpr int COLS = CD_THREADS / SPLIT;
+    constexpr int PER = 3 * DP + 4;                     // floats of a record
+    constexpr int ROW = PER + COLS;                     // a token in shared memory: its record, then v of the block's columns
+    constexpr int ROW4 = ROW / 4;
+    __shared__ __align__(16) float sm[2][CD_TOK][ROW];
     const int b = blockIdx.x, h = blockIdx.y;
-    const int tid = threadIdx.x, part = tid & (CD_SPLIT - 1);
-    const int col = blockIdx.z * CD_COLS + (tid >> 2);
+    const int tid = threadIdx.x, part = tid & (SPLIT - 1), cl = tid / SPLIT;
+    const int col0 = blockIdx.z * COLS, col = col0 + cl;
     const int dim = a.dim, vdim = a.vdim, H = a.H;
     const bool has_col = col < vdim;
     const int t0 = a.seq_start[b], t1 = a.seq_start[b + 1];
     if (t0 >= t1) return;
-    const int g = h / (H / a.G), gd = a.G * dim, C = 2 * gd + H * vdim;
+    const int VP = cd_vpitch(vdim);
     float* S = a.state + (size_t)a.slots[b] * a.state_stride + (size_t)h * dim * vdim;
     float s[RPT];
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int r = ((i >> 2) * CD_SPLIT + part) * 4 + (i & 3);
+        const int r = ((i >> 2) * SPLIT + part) * 4 + (i & 3);
         s[i] = (r < dim && has_col) ? S[(size_t)r * vdim + col] : 0.f;
     }
-    // the next token's vectors are asked for while this one is computed
-    float f[NF], v_r, beta_r, kq_r;
-    auto fetch = [&](int t) {
-#pragma unroll
-        for (int j = 0; j < NF; ++j) {
-            const int idx = tid + j * CD_THREADS, which = idx / DP, r = idx - which * DP;
-            float x = which == 2 ? 1.f : 0.f;
-            if (which < 3 && r < dim)
-                x = which == 0 ? a.qkv[(size_t)t * C + g * dim + r]
-                  : which == 1 ? a.qkv[(size_t)t * C + gd + g * dim + r]
-                               : a.decay[((size_t)t * H + h) * dim + r];
-            f[j] = x;
+    auto issue = [&](int ts, int par) {
+        const int ntok = min(CD_TOK, t1 - ts);
+        for (int idx = tid; idx < ntok * ROW4; idx += CD_THREADS) {
+            const int tt = idx / ROW4, e4 = idx - tt * ROW4;
+            const float* src = e4 < PER / 4 ? a.rec + ((size_t)(ts + tt) * H + h) * PER + e4 * 4
+                                            : a.vbuf + ((size_t)(ts + tt) * H + h) * VP + col0 + (e4 - PER / 4) * 4;
+            cp_async16((uint32_t)__cvta_generic_to_shared(&sm[par][tt][e4 * 4]), src);
         }
-        v_r = has_col ? a.qkv[(size_t)t * C + 2 * gd + (size_t)h * vdim + col] : 0.f;
-        beta_r = a.beta[(size_t)t * H + h];
-        kq_r = a.kq[(size_t)t * H + h];
+        cp_async_commit();
     };
-    fetch(t0);
-    for (int t = t0; t < t1; ++t) {
-        const int par = (t - t0) & 1;
-        float* stage = &sm[par][0][0];
+    issue(t0, 0);
+    for (int ts = t0, st = 0; ts < t1; ts += CD_TOK, ++st) {
+        const int par = st & 1;
+        cp_async_wait<0>();
+        __syncthreads();            // this stage has landed for everyone, and everyone is done with the stage before
+        if (ts + CD_TOK < t1) issue(ts + CD_TOK, par ^ 1);
+        const int ntok = min(CD_TOK, t1 - ts);
+        for (int tt = 0; tt < ntok; ++tt) {
+            const float* row = &sm[par][tt][0];
+            const float4* Q4 = reinterpret_cast<const float4*>(row);
+            const float4* K4 = reinterpret_cast<const float4*>(row + DP);
+            const float4* G4 = reinterpret_cast<const float4*>(row + 2 * DP);
+            float4 kk[RPT / 4];
+            float dk[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < NF; ++j) {
-            const int idx = tid + j * CD_THREADS;
-            if (idx < 3 * DP) stage[idx] = f[j];
-        }
-        const float v_c = v_r, beta_c = beta_r, kq_c = kq_r;
-        if (t + 1 < t1) fetch(t + 1);
-        __syncthreads();
-        const float4* Q4 = reinterpret_cast<const float4*>(&sm[par][0][0]);
-        const float4* K4 = reinterpret_cast<const float4*>(&sm[par][1][0]);
-        const float4* G4 = reinterpret_cast<const float4*>(&sm[par][2][0]);
-        float dk = 0.f, dq = 0.f;
+            for (int i4 = 0; i4 < RPT / 4; ++i4) {
+                const int ch = i4 * SPLIT + part;
+                const float4 q = Q4[ch], k = K4[ch], gg = G4[ch];
+                kk[i4] = k;
+                float* si = s + i4 * 4;
+                si[0] *= gg.x; si[1] *= gg.y; si[2] *= gg.z; si[3] *= gg.w;
+                dk[0] += si[0] * k.x; dk[1] += si[1] * k.y; dk[2] += si[2] * k.z; dk[3] += si[3] * k.w;
+                dq[0] += si[0] * q.x; dq[1] += si[1] * q.y; dq[2] += si[2] * q.z; dq[3] += si[3] * q.w;
+            }
+            float sk = (dk[0] + dk[1]) + (dk[2] + dk[3]), sq = (dq[0] + dq[1]) + (dq[2] + dq[3]);
 #pragma unroll
-        for (int i4 = 0; i4 < RPT / 4; ++i4) {
-            const int ch = i4 * CD_SPLIT + part;
-            const float4 q = Q4[ch], k = K4[ch], gg = G4[ch];
-            float* si = s + i4 * 4;
-            si[0] *= gg.x; si[1] *= gg.y; si[2] *= gg.z; si[3] *= gg.w;
-            dk += si[0] * k.x + si[1] * k.y + si[2] * k.z + si[3] * k.w;
-            dq += si[0] * q.x + si[1] * q.y + si[2] * q.z + si[3] * q.w;
-        }
-        dk += __shfl_xor_sync(0xffffffffu, dk, 1);
-        dq += __shfl_xor_sync(0xffffffffu, dq, 1);
-        dk += __shfl_xor_sync(0xffffffffu, dk, 2);
-        dq += __shfl_xor_sync(0xffffffffu, dq, 2);
-        const float u = beta_c * (v_c - dk);
+            for (int o = 1; o < SPLIT; o <<= 1) {
+                sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            }
+            const float u = row[3 * DP] * (row[PER + cl] - sk);         // beta (v - S^T k)
 #pragma unroll
-        for (int i4 = 0; i4 < RPT / 4; ++i4) {
-            const float4 k = K4[i4 * CD_SPLIT + part];
-            float* si = s + i4 * 4;
-            si[0] += k.x * u; si[1] += k.y * u; si[2] += k.z * u; si[3] += k.w * u;
+            for (int i4 = 0; i4 < RPT / 4; ++i4) {
+                float* si = s + i4 * 4;
+                si[0] += kk[i4].x * u; si[1] += kk[i4].y * u; si[2] += kk[i4].z * u; si[3] += kk[i4].w * u;
+            }
+            if (part == 0 && has_col) a.out[((size_t)(ts + tt) * H + h) * vdim + col] = sq + u * row[3 * DP + 1];
         }
-        if (part == 0 && has_col) a.out[((size_t)t * H + h) * vdim + col] = dq + u * kq_c;
     }
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int r = ((i >> 2) * CD_SPLIT + part) * 4 + (i & 3);
+        const int r = ((i >> 2) * SPLIT + part) * 4 + (i & 3);
         if (r < dim && has_col) S[(size_t)r * vdim + col] = s[i];
     }
 }
@@ -225,7 +246,7 @@ static int delta_prep_launch(const DeltaPrepArgs& p, int nt, int B, cudaStream_t
     if (nt < 0 || B < 0 || p.G <= 0 || p.H <= 0 || p.H % p.G || p.dim <= 0 || p.vdim <= 0) return TB_ERR_ARG;
     if (p.taps < 1 || p.taps > CD_MAX_TAPS) return TB_ERR_UNSUPPORTED;
     const int C = 2 * p.G * p.dim + p.H * p.vdim;
-    const size_t smem = (size_t)C * sizeof(float);
+    const size_t smem = (size_t)(2 * p.dim + p.H / p.G * p.vdim) * sizeof(float);
     if (smem > 200 * 1024) return TB_ERR_UNSUPPORTED;
     if (nt == 0) return 0;
     static size_t configured = 0;
@@ -234,7 +255,8 @@ static int delta_prep_launch(const DeltaPrepArgs& p, int nt, int B, cudaStream_t
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    TB_LAUNCH((delta_prep_kernel<T>), nt, 256, smem, s, p);
+    dim3 pgrid(nt, p.G);
+    TB_LAUNCH((delta_prep_kernel<T>), pgrid, 128, smem, s, p);
     int rc = tb_last_error();
     if (rc || p.update_state || p.taps == 1) return rc;
     dim3 grid(B, (C + 255) / 256);
@@ -242,17 +264,24 @@ static int delta_prep_launch(const DeltaPrepArgs& p, int nt, int B, cudaStream_t
     return tb_last_error();
 }
 
+template <int RPT, int SPLIT>
+static void delta_scan_go(const DeltaScanArgs& a, int B, cudaStream_t s) {
+    dim3 grid(B, a.H, (a.vdim + CD_THREADS / SPLIT - 1) / (CD_THREADS / SPLIT));
+    TB_LAUNCH((delta_scan_kernel<RPT, SPLIT>), grid, CD_THREADS, 0, s, a);
+}
+
 static int delta_scan_launch(const DeltaScanArgs& a, int B, cudaStream_t s) {
     if (B < 0 || a.G <= 0 || a.H <= 0 || a.H % a.G || a.dim <= 0 || a.vdim <= 0) return TB_ERR_ARG;
     if (a.dim > 256) return TB_ERR_UNSUPPORTED;
     if (B == 0) return 0;
-    dim3 grid(B, a.H, (a.vdim + CD_COLS - 1) / CD_COLS);
-    const int rpt = (a.dim + CD_SPLIT - 1) / CD_SPLIT;
-    if (rpt <= 4) TB_LAUNCH((delta_scan_kernel<4>), grid, CD_THREADS, 0, s, a);
-    else if (rpt <= 8) TB_LAUNCH((delta_scan_kernel<8>), grid, CD_THREADS, 0, s, a);
-    else if (rpt <= 16) TB_LAUNCH((delta_scan_kernel<16>), grid, CD_THREADS, 0, s, a);
-    else if (rpt <= 32) TB_LAUNCH((delta_scan_kernel<32>), grid, CD_THREADS, 0, s, a);
-    else TB_LAUNCH((delta_scan_kernel<64>), grid, CD_THREADS, 0, s, a);
+    // many lanes per column: the chain of one token is what a sequence waits for, and a scheduler wants two warps
+    switch (cd_rows(a.dim)) {
+        case 16: delta_scan_go<4, 4>(a, B, s); break;
+        case 32: delta_scan_go<4, 8>(a, B, s); break;
+        case 64: delta_scan_go<8, 8>(a, B, s); break;
+        case 128: delta_scan_go<8, 16>(a, B, s); break;
+        default: delta_scan_go<16, 16>(a, B, s); break;
+    }
     return tb_last_error();
 }
 
@@ -261,13 +290,15 @@ extern "C" {
 int tb_delta_state_size(int G, int H, int dim, int vdim, int taps) {
     return H * dim * vdim + (taps - 1) * (2 * G * dim + H * vdim);
 }
+// Floats of a (token, head) record and of a (token, head) row of values between the two kernels.
+int tb_delta_record_size(int dim) { return cd_record(dim); }
+int tb_delta_value_pitch(int vdim) { return cd_vpitch(vdim); }
 #define TB_DELTA_PREP(SFX, T)                                                                                         \
     int tb_delta_prep_##SFX(const void* z, int ldz, const float* wconv, float* state, const float* a,                 \
-                            const float* dt_bias, const float* A_log, const float* bz, float* qkv, float* decay,      \
-                            float* beta, float* kq, const int* tok_seq, const int* seq_start, const int* slots,       \
-                            int nt, int B, int G, int H, int dim, int vdim, int taps, int update_state,               \
-                            cudaStream_t s) {                                                                         \
-        DeltaPrepArgs p{z, wconv, state, a, dt_bias, A_log, bz, qkv, decay, beta, kq, tok_seq, seq_start, slots,      \
+                            const float* dt_bias, const float* A_log, const float* bz, float* rec, float* vbuf,       \
+                            const int* tok_seq, const int* seq_start, const int* slots, int nt, int B, int G, int H,  \
+                            int dim, int vdim, int taps, int update_state, cudaStream_t s) {                          \
+        DeltaPrepArgs p{z, wconv, state, a, dt_bias, A_log, bz, rec, vbuf, tok_seq, seq_start, slots,                 \
                         (long long)tb_delta_state_size(G, H, dim, vdim, taps), (long long)H * dim * vdim, ldz, G, H,  \
                         dim, vdim, taps, update_state};                                                               \
         return delta_prep_launch<T>(p, nt, B, s);                                                                     \
@@ -275,11 +306,11 @@ int tb_delta_state_size(int G, int H, int dim, int vdim, int taps) {
 TB_DELTA_PREP(f32, float)
 TB_DELTA_PREP(bf16, __nv_bfloat16)
 
-int tb_delta_scan(const float* qkv, const float* decay, const float* beta, const float* kq, float* state, float* out,
-                  const int* seq_start, const int* slots, int B, int G, int H, int dim, int vdim, int taps,
-                  cudaStream_t s) {
-    DeltaScanArgs a{qkv, decay, beta, kq, state, out, seq_start, slots,
-                    (long long)tb_delta_state_size(G, H, dim, vdim, taps), G, H, dim, vdim};
+int tb_delta_scan(const float* rec, const float* vbuf, float* state, float* out, const int* seq_start,
+                  const int* slots, int B, int G, int H, int dim, int vdim, int taps, cudaStream_t s) {
+    if ((((uintptr_t)rec | (uintptr_t)vbuf) & 15)) return TB_ERR_ARG;
+    DeltaScanArgs a{rec, vbuf, state, out, seq_start, slots, (long long)tb_delta_state_size(G, H, dim, vdim, taps), G, H,
+                    dim, vdim};
     return delta_scan_launch(a, B, s);
 }
 }

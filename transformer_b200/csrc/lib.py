@@ -65,9 +65,9 @@ _SIGNATURES: Dict[str, str] = {
     "tb_qknorm_rope_cache_f32": "pippfpppippppiiiiiii", "tb_qknorm_rope_cache_bf16": "pippfpppippppiiiiiii",
     "tb_attention_window_f32": "pppppppppppiiiiiiiiiiiiff", "tb_attention_window_bf16": "pppppppppppiiiiiiiiiiiiff",
     "tb_attention_window_mma_bf16": "pppppppppppiiiiiiiiiiiiff",
-    "tb_delta_prep_f32": "pipppppppppppppiiiiiiii",
-    "tb_delta_prep_bf16": "pipppppppppppppiiiiiiii",
-    "tb_delta_scan": "ppppppppiiiiii",
+    "tb_delta_prep_f32": "pipppppppppppiiiiiiii",
+    "tb_delta_prep_bf16": "pipppppppppppiiiiiiii",
+    "tb_delta_scan": "ppppppiiiiii",
     "tb_bias_glu_f32": "pppii", "tb_bias_glu_bf16": "pppii",
     "tb_add_bias_f32": "ppii", "tb_add_bias_bf16": "ppii",
 }
@@ -90,7 +90,7 @@ class TapeMap(ctypes.Structure):
     _fields_ = [("base", ctypes.c_ulonglong), ("size", ctypes.c_ulonglong), ("delta", ctypes.c_longlong)]
 
 
-_NO_STREAM = {"tb_attention_window_mma_tile_tokens": "ii", "tb_delta_state_size": "iiiii", "tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
+_NO_STREAM = {"tb_attention_window_mma_tile_tokens": "ii", "tb_delta_state_size": "iiiii", "tb_delta_record_size": "i", "tb_delta_value_pitch": "i", "tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
               "tb_attention_tc_tile_tokens": ""}
 
 _lock = threading.Lock()
@@ -382,6 +382,16 @@ def delta_state_size(kv_heads: int, heads: int, dim: int, vdim: int, taps: int) 
     """Floats of state that the delta-rule kernels keep per sequence (the heads' memories, then the convolution's
     last inputs)."""
     return library().tb_delta_state_size(kv_heads, heads, dim, vdim, taps)
+
+
+def delta_record_size(dim: int) -> int:
+    """Floats of the record that the delta rule's first kernel leaves the scan per (token, head)."""
+    return library().tb_delta_record_size(dim)
+
+
+def delta_value_pitch(vdim: int) -> int:
+    """Floats of a (token, head) row of values between the delta rule's two kernels."""
+    return library().tb_delta_value_pitch(vdim)
 
 
 def attention_window_mma_tile_tokens(nh: int, nkvh: int) -> int:

@@ -77,16 +77,15 @@ class ChannelDelta(Mixer):
         matmul_nt(z[:, self.C:self.C + self.ra], w["a2"], a)               # float out
         gz = ctx.scratch("delta.gz", (nt, self.hv), self.dtype)
         matmul_nt(z[:, self.C + self.ra:], w["g2"], gz)
-        qkv = ctx.scratch("delta.qkv", (nt, self.C), torch.float32)
-        decay = ctx.scratch("delta.decay", (nt, H * self.dim), torch.float32)
-        beta = ctx.scratch("delta.beta", (nt, H), torch.float32)
-        kq = ctx.scratch("delta.kq", (nt, H), torch.float32)
+        # what enters the recurrence, float: one record per (token, head) [q | k | decay | beta, k.q], and the values
+        rec = ctx.scratch("delta.rec", (nt, H, lib.delta_record_size(self.dim)), torch.float32)
+        vals = ctx.scratch("delta.v", (nt, H, lib.delta_value_pitch(self.vdim)), torch.float32)
         lib.call("tb_delta_prep_" + sfx, lib.ptr(z), self.z_width, lib.ptr(w["conv"]), lib.ptr(state), lib.ptr(a),
-                 lib.ptr(w["dt_bias"]), lib.ptr(w["A_log"]), lib.ptr(bz), lib.ptr(qkv), lib.ptr(decay), lib.ptr(beta),
-                 lib.ptr(kq), lib.ptr(ctx.tok_seq), lib.ptr(ctx.seq_start), lib.ptr(ctx.slots), nt, ctx.B, self.G, H,
+                 lib.ptr(w["dt_bias"]), lib.ptr(w["A_log"]), lib.ptr(bz), lib.ptr(rec), lib.ptr(vals),
+                 lib.ptr(ctx.tok_seq), lib.ptr(ctx.seq_start), lib.ptr(ctx.slots), nt, ctx.B, self.G, H,
                  self.dim, self.vdim, self.taps, 1 if ctx.decode else 0)
         o = ctx.scratch("delta.o", (nt, self.hv), torch.float32)
-        lib.call("tb_delta_scan", lib.ptr(qkv), lib.ptr(decay), lib.ptr(beta), lib.ptr(kq), lib.ptr(state), lib.ptr(o),
+        lib.call("tb_delta_scan", lib.ptr(rec), lib.ptr(vals), lib.ptr(state), lib.ptr(o),
                  lib.ptr(ctx.seq_start), lib.ptr(ctx.slots), ctx.B, self.G, H, self.dim, self.vdim, self.taps)
         y = ctx.scratch("delta.y", (nt, self.hv), self.dtype)
         lib.call("tb_mlstm_out_" + sfx, lib.ptr(o), lib.ptr(gz), self.hv, lib.ptr(w["norm"]), lib.ptr(y), nt, H,

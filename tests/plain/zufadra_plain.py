@@ -238,7 +238,7 @@ def channel_delta_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, ep
 # ----------------------------------------------------------------------------------------------
 def dense_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], store=None) -> torch.Tensor:
     a = silu(_keep(h @ w["gate"].T, store) + w["gate.b"]) * (_keep(h @ w["up"].T, store) + w["up.b"])
-    return _keep(_keep(_keep(a, store) @ w["down"].T, store) + w["down.b"], store)
+    return _keep(_keep(a, store) @ w["down"].T + w["down.b"], store)
 
 
 # ----------------------------------------------------------------------------------------------

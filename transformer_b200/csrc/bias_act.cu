@@ -1,28 +1,55 @@
 // Biases of a feed-forward whose projections have them, applied to the products' results.
 //
 //   h[t, c] = silu(gu[t, c] + b[c]) * (gu[t, di + c] + b[di + c])        the (gate, up) pair with its biases
-//   y[t, c] += b[c]                                                       the down projection's
 // Biases are float; the sums and the activation are float, one rounding at the store.
+// h may have more columns than di (ldh > di): column di is then set to one and the rest to zero, so that a down
+// projection whose weight carries its bias as column di adds it inside its own sum.
 #include "common.cuh"
 
 template <typename T>
 __global__ void __launch_bounds__(256) bias_glu_kernel(const T* __restrict__ gu, const float* __restrict__ bias,
-                                                       T* __restrict__ h, long long n, int di) {
+                                                       T* __restrict__ h, long long n, int di, int ldh) {
     pdl_sync();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const long long t = i / di;
-        const int c = (int)(i - t * di);
+        const long long t = i / ldh;
+        const int c = (int)(i - t * ldh);
+        if (c >= di) {
+            stf(h + i, c == di ? 1.f : 0.f);
+            continue;
+        }
         const float g = ldf(gu + t * 2 * di + c) + bias[c];
         const float u = ldf(gu + t * 2 * di + di + c) + bias[di + c];
         stf(h + i, g / (1.0f + expf(-g)) * u);
     }
 }
 
+// The same, eight entries per thread with 16-byte accesses (di and ldh multiples of 8).
 template <typename T>
-__global__ void __launch_bounds__(256) add_bias_kernel(T* __restrict__ y, const float* __restrict__ bias, long long n, int d) {
+__global__ void __launch_bounds__(256) bias_glu_vec_kernel(const T* __restrict__ gu, const float* __restrict__ bias,
+                                                           T* __restrict__ h, long long n8, int di, int ldh) {
     pdl_sync();
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-        stf(y + i, ldf(y + i) + bias[i % d]);
+    const int per_row = ldh / 8;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / per_row;
+        const int c = (int)(i - t * per_row) * 8;
+        float o[8];
+        if (c >= di) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = (c + e == di) ? 1.f : 0.f;
+        } else {
+            float g[8], u[8], bg[8], bu[8];
+            load8(gu + t * 2 * di + c, g);
+            load8(gu + t * 2 * di + di + c, u);
+            load8(bias + c, bg);
+            load8(bias + di + c, bu);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float a = g[e] + bg[e];
+                o[e] = a / (1.0f + expf(-a)) * (u[e] + bu[e]);
+            }
+        }
+        store8(h + t * ldh + c, o);
+    }
 }
 
 static int grid_for(long long n) {
@@ -32,18 +59,14 @@ static int grid_for(long long n) {
 
 extern "C" {
 #define TB_BIAS(SFX, T)                                                                                               \
-    int tb_bias_glu_##SFX(const void* gu, const float* bias, void* h, int nt, int di, cudaStream_t s) {               \
-        if (nt < 0 || di <= 0 || !bias) return TB_ERR_ARG;                                                            \
+    int tb_bias_glu_##SFX(const void* gu, const float* bias, void* h, int nt, int di, int ldh, cudaStream_t s) {      \
+        if (nt < 0 || di <= 0 || ldh < di || !bias) return TB_ERR_ARG;                                                \
         if (nt == 0) return 0;                                                                                        \
-        const long long n = (long long)nt * di;                                                                       \
-        TB_LAUNCH((bias_glu_kernel<T>), grid_for(n), 256, 0, s, (const T*)gu, bias, (T*)h, n, di);                    \
-        return tb_last_error();                                                                                       \
-    }                                                                                                                 \
-    int tb_add_bias_##SFX(void* y, const float* bias, int nt, int d, cudaStream_t s) {                                \
-        if (nt < 0 || d <= 0 || !bias) return TB_ERR_ARG;                                                             \
-        if (nt == 0) return 0;                                                                                        \
-        const long long n = (long long)nt * d;                                                                        \
-        TB_LAUNCH((add_bias_kernel<T>), grid_for(n), 256, 0, s, (T*)y, bias, n, d);                                   \
+        const long long n = (long long)nt * ldh;                                                                      \
+        if (di % 8 == 0 && ldh % 8 == 0 && (((uintptr_t)gu | (uintptr_t)h | (uintptr_t)bias) & 15) == 0)              \
+            TB_LAUNCH((bias_glu_vec_kernel<T>), grid_for(n / 8), 256, 0, s, (const T*)gu, bias, (T*)h, n / 8, di, ldh); \
+        else                                                                                                          \
+            TB_LAUNCH((bias_glu_kernel<T>), grid_for(n), 256, 0, s, (const T*)gu, bias, (T*)h, n, di, ldh);           \
         return tb_last_error();                                                                                       \
     }
 TB_BIAS(f32, float)
@@ -53,5 +76,3 @@ TB_BIAS(bf16, __nv_bfloat16)
 #include "tape.h"
 TB_TAPE_REGISTER(tb_bias_glu_f32)
 TB_TAPE_REGISTER(tb_bias_glu_bf16)
-TB_TAPE_REGISTER(tb_add_bias_f32)
-TB_TAPE_REGISTER(tb_add_bias_bf16)

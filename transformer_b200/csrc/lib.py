@@ -68,8 +68,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_delta_prep_f32": "pipppppppppppiiiiiiii",
     "tb_delta_prep_bf16": "pipppppppppppiiiiiiii",
     "tb_delta_scan": "ppppppiiiiii",
-    "tb_bias_glu_f32": "pppii", "tb_bias_glu_bf16": "pppii",
-    "tb_add_bias_f32": "ppii", "tb_add_bias_bf16": "ppii",
+    "tb_bias_glu_f32": "pppiii", "tb_bias_glu_bf16": "pppiii",
 }
 class TapeArg(ctypes.Union):
     _fields_ = [("p", ctypes.c_void_p), ("i", ctypes.c_int), ("f", ctypes.c_float), ("l", ctypes.c_longlong),

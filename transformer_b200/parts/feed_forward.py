@@ -22,7 +22,9 @@ ROUTER_TAIL_ROWS = 256      # up to this many tokens the norm before the experts
 class DenseSwiGLU(FeedForward):
     """params: width, di, bias (default False).  gate_up = x1 Wgu^T (gate rows first), h = silu(gate) * up,
     out = h Wd^T (compute.rs:278-292).  With ``bias`` all three projections have one: ``bgu`` (gate's, then up's)
-    and ``bd``, float."""
+    and ``bd``, float.  The down projection's bias rides inside its product: the bound weight gets the bias as one
+    more column (and zeros up to a multiple of eight), and the kernel that applies the pair's biases and the
+    activation writes a one into that column of ``h``."""
     graph_safe = True
     launches_only = True
 
@@ -39,17 +41,25 @@ class DenseSwiGLU(FeedForward):
             decl["bd"] = ParamDecl((self.d,), "norm", "normal")
         return decl
 
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if self.bias:
+            wd, bd = self.weights["wd"], self.weights.pop("bd")
+            pad = (self.di + 1 + 7) // 8 * 8 - self.di - 1
+            self.weights["wd"] = torch.cat([wd, bd.to(wd.dtype)[:, None], wd.new_zeros((self.d, pad))], dim=1).contiguous()
+
     def forward(self, ctx, x1, out) -> None:
         nt = x1.shape[0]
-        h = ctx.scratch("ff.h", (nt, self.di), self.dtype)
         if self.bias:
-            sfx = lib.suffix(self.dtype)
+            wide = self.weights["wd"].shape[1]
             gu = ctx.scratch("ff.gu", (nt, 2 * self.di), self.dtype)
             matmul_nt(x1, self.weights["wgu"], gu)
-            lib.call("tb_bias_glu_" + sfx, lib.ptr(gu), lib.ptr(self.weights["bgu"]), lib.ptr(h), nt, self.di)
+            h = ctx.scratch("ff.h1", (nt, wide), self.dtype)
+            lib.call("tb_bias_glu_" + lib.suffix(self.dtype), lib.ptr(gu), lib.ptr(self.weights["bgu"]), lib.ptr(h), nt,
+                     self.di, wide)
             matmul_nt(h, self.weights["wd"], out)
-            lib.call("tb_add_bias_" + sfx, lib.ptr(out), lib.ptr(self.weights["bd"]), nt, self.d)
             return
+        h = ctx.scratch("ff.h", (nt, self.di), self.dtype)
         grouped_matmul(x1, self.weights["wgu"], h, swiglu=True)
         matmul_nt(h, self.weights["wd"], out)
 

@@ -408,7 +408,7 @@ def test_delta_rule_kernel_keeps_a_token_for_hundreds_of_steps(G, H, dim, vdim):
         # device copies stay in names until the kernel has run: a temporary's memory would be handed to the next one
         d_rec, d_vals, starts, slots = rec.cuda(), vals.cuda(), I([0, n]), I([slot])
         lib.call("tb_delta_scan", lib.ptr(d_rec), lib.ptr(d_vals), lib.ptr(state), lib.ptr(out),
-                 lib.ptr(starts), lib.ptr(slots), 1, G, H, dim, vdim, taps)
+                 lib.ptr(starts), lib.ptr(slots), n, 1, G, H, dim, vdim, taps)
         torch.cuda.synchronize()
         return out.cpu()
 

@@ -16,7 +16,7 @@
 // the gate; that is how a few decoding sequences fill the GPU.
 //
 // The cap's tanh is 1 - 2 / (1 + 2^(2 y log2 e)) with the hardware's exponential and reciprocal (absolute error
-// of a few 1e-7, times the cap).  Head sizes: the instantiations at the end; others answer TB_ERR_UNSUPPORTED and
+// of a few 1e-7, times the cap), its constants folded with the score's multiplier and log2 e.  Head sizes: the instantiations at the end; others answer TB_ERR_UNSUPPORTED and
 // the caller takes the general kernel.
 #include "attention_prefill.cuh"
 
@@ -41,11 +41,6 @@ struct WinMmaArgs {
 };
 
 __host__ __device__ constexpr int wm_blocks(int dk, int dv) { return (dk + dv) <= 256 ? 3 : 1; }
-
-__device__ __forceinline__ float wm_tanh(float y) {
-    // 1 - 2 / (1 + e^{2y}); e^{2y} = 2^(y * 2 log2 e): inf for large y (result 1), 0 for very negative y (result -1)
-    return 1.0f - __fdividef(2.0f, 1.0f + exp2f(y * 2.885390081777927f));
-}
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(WM_THREADS, wm_blocks(DK, DV)) attention_window_mma_kernel(const WinMmaArgs a) {
@@ -119,8 +114,9 @@ __global__ void __launch_bounds__(WM_THREADS, wm_blocks(DK, DV)) attention_windo
     const int row_a = warp * 16 + gid, row_b = row_a + 8;
     const int pos_a = pos_first + row_a / group, pos_b = pos_first + row_b / group;
     const uint32_t sq_addr = (uint32_t)__cvta_generic_to_shared(sq);
-    const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
     const float LOG2E = 1.4426950408889634f;
+    const float scale_l2 = a.scale * LOG2E, cap_l2 = a.softcap * LOG2E;
+    const float pre_cap = a.softcap > 0.f ? a.scale / a.softcap * 2.0f * LOG2E : 0.f;
 
     for (int it = i_lo; it < i_hi; ++it) {
         const int buf = (it - i_lo) & 1;
@@ -168,9 +164,9 @@ __global__ void __launch_bounds__(WM_THREADS, wm_blocks(DK, DV)) attention_windo
             for (int nb = 0; nb < WM_KEYS / 8; ++nb) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    float v = s[nb][c] * a.scale;
-                    if (a.softcap > 0.f) v = a.softcap * wm_tanh(v * inv_cap);
-                    v *= LOG2E;
+                    // score * log2 e, capped: cap tanh(y) = cap - 2 cap / (1 + e^{2y}), y = s * scale / cap
+                    float v = a.softcap > 0.f ? cap_l2 - __fdividef(2.0f * cap_l2, 1.0f + exp2f(s[nb][c] * pre_cap))
+                                              : s[nb][c] * scale_l2;
                     if (!open) {
                         const int key = key0 + nb * 8 + tid4 * 2 + (c & 1);
                         const int pos = (c & 2) ? pos_b : pos_a;

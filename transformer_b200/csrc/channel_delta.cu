@@ -53,77 +53,86 @@ struct DeltaPrepArgs {
 
 __device__ __forceinline__ float cd_softplus(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
-// A block = one token x one key head g: the convolutions of that head's query and key channels and of the value
-// channels of the heads that read it, the two unit norms, and those heads' decays and betas.
+// A block = four consecutive tokens of the step x one key head g: the convolutions of that head's query and key
+// channels and of the value channels of the heads that read it (a thread keeps a channel's taps for the four tokens),
+// then a warp per token: the two unit norms, k . q, and those heads' values, decays and betas.
+#define CD_PT 4
 template <typename T>
-__global__ void __launch_bounds__(128) delta_prep_kernel(const DeltaPrepArgs p) {
+__global__ void __launch_bounds__(32 * CD_PT) delta_prep_kernel(const DeltaPrepArgs p, int nt) {
     pdl_sync();
-    extern __shared__ float y[];        // [2 dim + per vdim] the convolution's outputs after silu: q, k, v of the group
-    const int t = blockIdx.x, g = blockIdx.y;
-    const int b = p.tok_seq[t];
-    const int li = t - p.seq_start[b];                  // index of the token among its sequence's tokens of the step
+    extern __shared__ float y_all[];    // [CD_PT][2 dim + per vdim] the convolution's outputs after silu: q, k, v of the group
+    const int tb = blockIdx.x * CD_PT, g = blockIdx.y;
+    const int ntok = min(CD_PT, nt - tb);
     const int dim = p.dim, vdim = p.vdim, gd = p.G * dim, per = p.H / p.G, taps = p.taps;
     const int C = 2 * gd + p.H * vdim, n_loc = 2 * dim + per * vdim;
     const int DP = cd_rows(dim), PER = cd_record(dim), VP = cd_vpitch(vdim);
     const T* z = static_cast<const T*>(p.z);
-    float* cs = p.state + (size_t)p.slots[b] * p.state_stride + p.conv_offset;     // [taps - 1][C]
+    int li[CD_PT];                      // index of each token among its sequence's tokens of the step
+    float* cs[CD_PT];                   // its sequence's convolution state [taps - 1][C]
+#pragma unroll
+    for (int tt = 0; tt < CD_PT; ++tt) {
+        li[tt] = 0;
+        cs[tt] = nullptr;
+        if (tt < ntok) {
+            const int b = p.tok_seq[tb + tt];
+            li[tt] = tb + tt - p.seq_start[b];
+            cs[tt] = p.state + (size_t)p.slots[b] * p.state_stride + p.conv_offset;
+        }
+    }
     for (int i = threadIdx.x; i < n_loc; i += blockDim.x) {
         // local entry i -> channel c of the row
         const int c = i < dim ? g * dim + i : i < 2 * dim ? gd + g * dim + (i - dim) : 2 * gd + g * per * vdim + (i - 2 * dim);
-        float acc = 0.f, old[CD_MAX_TAPS];
-        for (int j = 0; j < taps; ++j) {
-            const int back = taps - 1 - j, s = li - back;
-            const float x = s >= 0 ? ldf(z + (size_t)(t - back) * p.ldz + c) : cs[(size_t)(taps - 1 + s) * C + c];
-            old[j] = x;
-            acc += p.wconv[(size_t)c * taps + j] * x;
+        float w[CD_MAX_TAPS];
+        for (int j = 0; j < taps; ++j) w[j] = p.wconv[(size_t)c * taps + j];
+#pragma unroll
+        for (int tt = 0; tt < CD_PT; ++tt) {
+            if (tt >= ntok) break;
+            const int t = tb + tt;
+            float acc = 0.f, old[CD_MAX_TAPS];
+            for (int j = 0; j < taps; ++j) {
+                const int back = taps - 1 - j, s = li[tt] - back;
+                const float x = s >= 0 ? ldf(z + (size_t)(t - back) * p.ldz + c) : cs[tt][(size_t)(taps - 1 + s) * C + c];
+                old[j] = x;
+                acc += w[j] * x;
+            }
+            y_all[tt * n_loc + i] = acc / (1.0f + expf(-acc));
+            if (p.update_state)     // a step of one token per sequence: this thread alone touches its channel's state
+                for (int r = 0; r + 1 < taps; ++r) cs[tt][(size_t)r * C + c] = old[r + 1];
         }
-        y[i] = acc / (1.0f + expf(-acc));
-        if (p.update_state)         // a step of one token per sequence: this thread alone touches its channel's state
-            for (int r = 0; r + 1 < taps; ++r) cs[(size_t)r * C + c] = old[r + 1];
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, tt = threadIdx.x >> 5;
+    if (tt >= ntok) return;
+    const int t = tb + tt;
+    const float* y = y_all + tt * n_loc;
     float* rec = p.rec + ((size_t)t * p.H + (size_t)g * per) * PER;          // the group's first head
-    if (warp == 0) {
-        const float* q = y;
-        const float* k = y + dim;
-        float sq = 0.f, sk = 0.f, dot = 0.f;
-        for (int c = lane; c < dim; c += 32) {
-            sq += q[c] * q[c];
-            sk += k[c] * k[c];
-            dot += q[c] * k[c];
-        }
-        sq = warp_sum(sq);
-        sk = warp_sum(sk);
-        dot = warp_sum(dot);
-        const float iq = rsqrtf((float)dim) / sqrtf(sq + CD_UNIT_EPS), ik = 1.0f / sqrtf(sk + CD_UNIT_EPS);
-        for (int h = 0; h < per; ++h) {
-            float* r = rec + (size_t)h * PER;
-            for (int c = lane; c < DP; c += 32) {
-                r[c] = c < dim ? q[c] * iq : 0.f;
-                r[DP + c] = c < dim ? k[c] * ik : 0.f;
-            }
-            if (lane < 4) {
-                const int hh = g * per + h;
-                r[3 * DP + lane] = lane == 0 ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + hh])) : lane == 1 ? dot * iq * ik : 0.f;
-            }
-        }
-    } else {
-        const int nth = blockDim.x - 32, id = threadIdx.x - 32;
-        float* vb = p.vbuf + ((size_t)t * p.H + (size_t)g * per) * VP;
-        for (int i = id; i < per * VP; i += nth) {
-            const int h = i / VP, c = i - h * VP;
-            vb[i] = c < vdim ? y[2 * dim + h * vdim + c] : 0.f;
-        }
-        for (int i = id; i < per * DP; i += nth) {
-            const int h = i / DP, c = i - h * DP;
+    const float* q = y;
+    const float* k = y + dim;
+    float sq = 0.f, sk = 0.f, dot = 0.f;
+    for (int c = lane; c < dim; c += 32) {
+        sq += q[c] * q[c];
+        sk += k[c] * k[c];
+        dot += q[c] * k[c];
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    dot = warp_sum(dot);
+    const float iq = rsqrtf((float)dim) / sqrtf(sq + CD_UNIT_EPS), ik = 1.0f / sqrtf(sk + CD_UNIT_EPS);
+    float* vb = p.vbuf + ((size_t)t * p.H + (size_t)g * per) * VP;
+    for (int h = 0; h < per; ++h) {
+        float* r = rec + (size_t)h * PER;
+        const int hh = g * per + h;
+        const float rate = expf(p.A_log[hh]);
+        for (int c = lane; c < DP; c += 32) {
             float gval = 1.f;
-            if (c < dim) {
-                const int hd = (g * per + h) * dim + c;     // (head, key channel)
-                gval = expf(-expf(p.A_log[hd / dim]) * cd_softplus(p.a[(size_t)t * p.H * dim + hd] + p.dt_bias[hd]));
-            }
-            rec[(size_t)h * PER + 2 * DP + c] = gval;
+            if (c < dim) gval = expf(-rate * cd_softplus(p.a[(size_t)t * p.H * dim + hh * dim + c] + p.dt_bias[hh * dim + c]));
+            r[c] = c < dim ? q[c] * iq : 0.f;
+            r[DP + c] = c < dim ? k[c] * ik : 0.f;
+            r[2 * DP + c] = gval;
         }
+        if (lane < 4)
+            r[3 * DP + lane] = lane == 0 ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + hh])) : lane == 1 ? dot * iq * ik : 0.f;
+        for (int c = lane; c < VP; c += 32) vb[(size_t)h * VP + c] = c < vdim ? y[2 * dim + h * vdim + c] : 0.f;
     }
 }
 
@@ -246,7 +255,7 @@ static int delta_prep_launch(const DeltaPrepArgs& p, int nt, int B, cudaStream_t
     if (nt < 0 || B < 0 || p.G <= 0 || p.H <= 0 || p.H % p.G || p.dim <= 0 || p.vdim <= 0) return TB_ERR_ARG;
     if (p.taps < 1 || p.taps > CD_MAX_TAPS) return TB_ERR_UNSUPPORTED;
     const int C = 2 * p.G * p.dim + p.H * p.vdim;
-    const size_t smem = (size_t)(2 * p.dim + p.H / p.G * p.vdim) * sizeof(float);
+    const size_t smem = (size_t)CD_PT * (2 * p.dim + p.H / p.G * p.vdim) * sizeof(float);
     if (smem > 200 * 1024) return TB_ERR_UNSUPPORTED;
     if (nt == 0) return 0;
     static size_t configured = 0;
@@ -255,8 +264,8 @@ static int delta_prep_launch(const DeltaPrepArgs& p, int nt, int B, cudaStream_t
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    dim3 pgrid(nt, p.G);
-    TB_LAUNCH((delta_prep_kernel<T>), pgrid, 128, smem, s, p);
+    dim3 pgrid((nt + CD_PT - 1) / CD_PT, p.G);
+    TB_LAUNCH((delta_prep_kernel<T>), pgrid, 32 * CD_PT, smem, s, p, nt);
     int rc = tb_last_error();
     if (rc || p.update_state || p.taps == 1) return rc;
     dim3 grid(B, (C + 255) / 256);
@@ -264,23 +273,41 @@ static int delta_prep_launch(const DeltaPrepArgs& p, int nt, int B, cudaStream_t
     return tb_last_error();
 }
 
+static int cd_scan_lanes_override = 0;      // measurements: lanes per column whatever the batch (0: by the rule below)
+
 template <int RPT, int SPLIT>
 static void delta_scan_go(const DeltaScanArgs& a, int B, cudaStream_t s) {
     dim3 grid(B, a.H, (a.vdim + CD_THREADS / SPLIT - 1) / (CD_THREADS / SPLIT));
     TB_LAUNCH((delta_scan_kernel<RPT, SPLIT>), grid, CD_THREADS, 0, s, a);
 }
 
-static int delta_scan_launch(const DeltaScanArgs& a, int B, cudaStream_t s) {
+static int delta_scan_launch(const DeltaScanArgs& a, int nt, int B, cudaStream_t s) {
     if (B < 0 || a.G <= 0 || a.H <= 0 || a.H % a.G || a.dim <= 0 || a.vdim <= 0) return TB_ERR_ARG;
     if (a.dim > 256) return TB_ERR_UNSUPPORTED;
     if (B == 0) return 0;
-    // many lanes per column: the chain of one token is what a sequence waits for, and a scheduler wants two warps
-    switch (cd_rows(a.dim)) {
-        case 16: delta_scan_go<4, 4>(a, B, s); break;
-        case 32: delta_scan_go<4, 8>(a, B, s); break;
-        case 64: delta_scan_go<8, 8>(a, B, s); break;
-        case 128: delta_scan_go<8, 16>(a, B, s); break;
-        default: delta_scan_go<16, 16>(a, B, s); break;
+    // Lanes per column.  Prompts: many lanes, since the chain of one token is what a sequence waits for (measured
+    // with 16 heads of 128 x 128: one prompt of 2,048 tokens 0.71 ms with 16 lanes, 0.87 with 4; eight of 1,024
+    // tokens 1.32 against 1.65).  Steps of a token or two per sequence: four lanes, since then the kernel is the
+    // state's way in and out of the registers, and a thread's rows lie closer together (batch 64: 44 against 103 us).
+    const int rows = cd_rows(a.dim);
+    int lanes = rows >= 128 ? 16 : rows >= 32 ? 8 : 4;
+    if (cd_scan_lanes_override > 0) lanes = cd_scan_lanes_override;
+    else if (nt <= 2 * B) lanes = 4;
+    if (lanes > rows / 4) lanes = rows / 4;
+    if (rows / lanes > 32) lanes = rows / 32;
+    switch (rows / lanes * 100 + lanes) {       // rows per thread, lanes per column
+        case 4 * 100 + 4: delta_scan_go<4, 4>(a, B, s); break;
+        case 8 * 100 + 4: delta_scan_go<8, 4>(a, B, s); break;
+        case 4 * 100 + 8: delta_scan_go<4, 8>(a, B, s); break;
+        case 16 * 100 + 4: delta_scan_go<16, 4>(a, B, s); break;
+        case 8 * 100 + 8: delta_scan_go<8, 8>(a, B, s); break;
+        case 4 * 100 + 16: delta_scan_go<4, 16>(a, B, s); break;
+        case 32 * 100 + 4: delta_scan_go<32, 4>(a, B, s); break;
+        case 16 * 100 + 8: delta_scan_go<16, 8>(a, B, s); break;
+        case 8 * 100 + 16: delta_scan_go<8, 16>(a, B, s); break;
+        case 32 * 100 + 8: delta_scan_go<32, 8>(a, B, s); break;
+        case 16 * 100 + 16: delta_scan_go<16, 16>(a, B, s); break;
+        default: return TB_ERR_UNSUPPORTED;
     }
     return tb_last_error();
 }
@@ -289,6 +316,11 @@ extern "C" {
 // Floats of state per slot: the matrix memory of every head, then the convolution's last inputs.
 int tb_delta_state_size(int G, int H, int dim, int vdim, int taps) {
     return H * dim * vdim + (taps - 1) * (2 * G * dim + H * vdim);
+}
+// For measurements: 4, 8 or 16 lanes per column in the scan whatever the batch; 0 gives the choice back to the rule.
+int tb_delta_scan_lanes(int lanes) {
+    cd_scan_lanes_override = lanes;
+    return 0;
 }
 // Floats of a (token, head) record and of a (token, head) row of values between the two kernels.
 int tb_delta_record_size(int dim) { return cd_record(dim); }
@@ -307,11 +339,11 @@ TB_DELTA_PREP(f32, float)
 TB_DELTA_PREP(bf16, __nv_bfloat16)
 
 int tb_delta_scan(const float* rec, const float* vbuf, float* state, float* out, const int* seq_start,
-                  const int* slots, int B, int G, int H, int dim, int vdim, int taps, cudaStream_t s) {
+                  const int* slots, int nt, int B, int G, int H, int dim, int vdim, int taps, cudaStream_t s) {
     if ((((uintptr_t)rec | (uintptr_t)vbuf) & 15)) return TB_ERR_ARG;
     DeltaScanArgs a{rec, vbuf, state, out, seq_start, slots, (long long)tb_delta_state_size(G, H, dim, vdim, taps), G, H,
                     dim, vdim};
-    return delta_scan_launch(a, B, s);
+    return delta_scan_launch(a, nt, B, s);
 }
 }
 

@@ -67,7 +67,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_attention_window_mma_bf16": "pppppppppppiiiiiiiiiiiiff",
     "tb_delta_prep_f32": "pipppppppppppiiiiiiii",
     "tb_delta_prep_bf16": "pipppppppppppiiiiiiii",
-    "tb_delta_scan": "ppppppiiiiii",
+    "tb_delta_scan": "ppppppiiiiiii",
     "tb_bias_glu_f32": "pppiii", "tb_bias_glu_bf16": "pppiii",
 }
 class TapeArg(ctypes.Union):
@@ -89,7 +89,7 @@ class TapeMap(ctypes.Structure):
     _fields_ = [("base", ctypes.c_ulonglong), ("size", ctypes.c_ulonglong), ("delta", ctypes.c_longlong)]
 
 
-_NO_STREAM = {"tb_attention_window_mma_tile_tokens": "ii", "tb_delta_state_size": "iiiii", "tb_delta_record_size": "i", "tb_delta_value_pitch": "i", "tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
+_NO_STREAM = {"tb_attention_window_mma_tile_tokens": "ii", "tb_delta_state_size": "iiiii", "tb_delta_record_size": "i", "tb_delta_scan_lanes": "i", "tb_delta_value_pitch": "i", "tb_mlstm_state_size": "ii", "tb_latent_attention_tile_tokens": "i", "tb_attention_tile_tokens": "ii", "tb_gemm_tc_status": "", "tb_attention_prefill_tile_tokens": "",
               "tb_attention_tc_tile_tokens": ""}
 
 _lock = threading.Lock()

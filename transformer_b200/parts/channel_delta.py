@@ -86,7 +86,7 @@ class ChannelDelta(Mixer):
                  self.dim, self.vdim, self.taps, 1 if ctx.decode else 0)
         o = ctx.scratch("delta.o", (nt, self.hv), torch.float32)
         lib.call("tb_delta_scan", lib.ptr(rec), lib.ptr(vals), lib.ptr(state), lib.ptr(o),
-                 lib.ptr(ctx.seq_start), lib.ptr(ctx.slots), ctx.B, self.G, H, self.dim, self.vdim, self.taps)
+                 lib.ptr(ctx.seq_start), lib.ptr(ctx.slots), nt, ctx.B, self.G, H, self.dim, self.vdim, self.taps)
         y = ctx.scratch("delta.y", (nt, self.hv), self.dtype)
         lib.call("tb_mlstm_out_" + sfx, lib.ptr(o), lib.ptr(gz), self.hv, lib.ptr(w["norm"]), lib.ptr(y), nt, H,
                  self.vdim, self.eps)

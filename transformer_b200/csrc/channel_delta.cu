@@ -276,9 +276,12 @@ static int delta_prep_launch(const DeltaPrepArgs& p, int nt, int B, cudaStream_t
 static int cd_scan_lanes_override = 0;      // measurements: lanes per column whatever the batch (0: by the rule below)
 
 template <int RPT, int SPLIT>
-static void delta_scan_go(const DeltaScanArgs& a, int B, cudaStream_t s) {
+static void delta_scan_go(const DeltaScanArgs& a, int B, bool early, cudaStream_t s) {
     dim3 grid(B, a.H, (a.vdim + CD_THREADS / SPLIT - 1) / (CD_THREADS / SPLIT));
-    TB_LAUNCH((delta_scan_kernel<RPT, SPLIT>), grid, CD_THREADS, 0, s, a);
+    if (early)
+        TB_LAUNCH((delta_scan_kernel<RPT, SPLIT>), grid, CD_THREADS, 0, s, a);
+    else        // prompts: the blocks run for the whole sequence and want an SM each (see tb_launch_plain)
+        tb_launch_plain(delta_scan_kernel<RPT, SPLIT>, grid, dim3(CD_THREADS), 0, s, a);
 }
 
 static int delta_scan_launch(const DeltaScanArgs& a, int nt, int B, cudaStream_t s) {
@@ -293,20 +296,21 @@ static int delta_scan_launch(const DeltaScanArgs& a, int nt, int B, cudaStream_t
     int lanes = rows >= 128 ? 16 : rows >= 32 ? 8 : 4;
     if (cd_scan_lanes_override > 0) lanes = cd_scan_lanes_override;
     else if (nt <= 2 * B) lanes = 4;
+    const bool early = nt <= 2 * B;
     if (lanes > rows / 4) lanes = rows / 4;
     if (rows / lanes > 32) lanes = rows / 32;
     switch (rows / lanes * 100 + lanes) {       // rows per thread, lanes per column
-        case 4 * 100 + 4: delta_scan_go<4, 4>(a, B, s); break;
-        case 8 * 100 + 4: delta_scan_go<8, 4>(a, B, s); break;
-        case 4 * 100 + 8: delta_scan_go<4, 8>(a, B, s); break;
-        case 16 * 100 + 4: delta_scan_go<16, 4>(a, B, s); break;
-        case 8 * 100 + 8: delta_scan_go<8, 8>(a, B, s); break;
-        case 4 * 100 + 16: delta_scan_go<4, 16>(a, B, s); break;
-        case 32 * 100 + 4: delta_scan_go<32, 4>(a, B, s); break;
-        case 16 * 100 + 8: delta_scan_go<16, 8>(a, B, s); break;
-        case 8 * 100 + 16: delta_scan_go<8, 16>(a, B, s); break;
-        case 32 * 100 + 8: delta_scan_go<32, 8>(a, B, s); break;
-        case 16 * 100 + 16: delta_scan_go<16, 16>(a, B, s); break;
+        case 4 * 100 + 4: delta_scan_go<4, 4>(a, B, early, s); break;
+        case 8 * 100 + 4: delta_scan_go<8, 4>(a, B, early, s); break;
+        case 4 * 100 + 8: delta_scan_go<4, 8>(a, B, early, s); break;
+        case 16 * 100 + 4: delta_scan_go<16, 4>(a, B, early, s); break;
+        case 8 * 100 + 8: delta_scan_go<8, 8>(a, B, early, s); break;
+        case 4 * 100 + 16: delta_scan_go<4, 16>(a, B, early, s); break;
+        case 32 * 100 + 4: delta_scan_go<32, 4>(a, B, early, s); break;
+        case 16 * 100 + 8: delta_scan_go<16, 8>(a, B, early, s); break;
+        case 8 * 100 + 16: delta_scan_go<8, 16>(a, B, early, s); break;
+        case 32 * 100 + 8: delta_scan_go<32, 8>(a, B, early, s); break;
+        case 16 * 100 + 16: delta_scan_go<16, 16>(a, B, early, s); break;
         default: return TB_ERR_UNSUPPORTED;
     }
     return tb_last_error();

@@ -227,6 +227,21 @@ static inline void tb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block
 #define TB_LAUNCH(kernel, grid, block, smem, stream, ...) \
     tb_launch_pdl(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, __VA_ARGS__)
 
+// The same without the early start: the kernel's blocks are placed only when the kernel before it has ended.  For a
+// long-running kernel of few blocks, which wants them spread over all SMs: started early, its blocks settle on
+// whichever SMs the kernel before it has left room on, several to an SM, and stay there.
+template <typename... KArgs, typename... Args>
+static inline void tb_launch_plain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                   Args... args) {
+    tb_state_carveout((const void*)kernel, block.x * block.y * block.z, smem);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int tb_last_error() {
     const int launch = (int)cudaGetLastError(), pending = tb_pending_error();
     tb_pending_error() = 0;

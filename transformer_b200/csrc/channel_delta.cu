@@ -53,16 +53,18 @@ struct DeltaPrepArgs {
 
 __device__ __forceinline__ float cd_softplus(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
-// A block = four consecutive tokens of the step x one key head g: the convolutions of that head's query and key
-// channels and of the value channels of the heads that read it (a thread keeps a channel's taps for the four tokens),
-// then a warp per token: the two unit norms, k . q, and those heads' values, decays and betas.
+// A block = up to four consecutive tokens of the step x one key head g: the convolutions of that head's query and
+// key channels and of the value channels of the heads that read it (a thread keeps a channel's taps for the block's
+// tokens), a warp per token for the two unit norms and k . q, then all threads write the group's records: q, k,
+// decays, betas, and the values.  Four tokens a block for prompts, one for steps of few tokens (more blocks).
 #define CD_PT 4
 template <typename T>
-__global__ void __launch_bounds__(32 * CD_PT) delta_prep_kernel(const DeltaPrepArgs p, int nt) {
+__global__ void __launch_bounds__(32 * CD_PT) delta_prep_kernel(const DeltaPrepArgs p, int nt, int pt) {
     pdl_sync();
-    extern __shared__ float y_all[];    // [CD_PT][2 dim + per vdim] the convolution's outputs after silu: q, k, v of the group
-    const int tb = blockIdx.x * CD_PT, g = blockIdx.y;
-    const int ntok = min(CD_PT, nt - tb);
+    extern __shared__ float y_all[];    // [pt][2 dim + per vdim] the convolution's outputs after silu: q, k, v of the group
+    __shared__ float stats[CD_PT][3];   // per token: the query's and the key's multiplier, k . q
+    const int tb = blockIdx.x * pt, g = blockIdx.y;
+    const int ntok = min(pt, nt - tb);
     const int dim = p.dim, vdim = p.vdim, gd = p.G * dim, per = p.H / p.G, taps = p.taps;
     const int C = 2 * gd + p.H * vdim, n_loc = 2 * dim + per * vdim;
     const int DP = cd_rows(dim), PER = cd_record(dim), VP = cd_vpitch(vdim);
@@ -101,38 +103,51 @@ __global__ void __launch_bounds__(32 * CD_PT) delta_prep_kernel(const DeltaPrepA
         }
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31, tt = threadIdx.x >> 5;
-    if (tt >= ntok) return;
-    const int t = tb + tt;
-    const float* y = y_all + tt * n_loc;
-    float* rec = p.rec + ((size_t)t * p.H + (size_t)g * per) * PER;          // the group's first head
-    const float* q = y;
-    const float* k = y + dim;
-    float sq = 0.f, sk = 0.f, dot = 0.f;
-    for (int c = lane; c < dim; c += 32) {
-        sq += q[c] * q[c];
-        sk += k[c] * k[c];
-        dot += q[c] * k[c];
-    }
-    sq = warp_sum(sq);
-    sk = warp_sum(sk);
-    dot = warp_sum(dot);
-    const float iq = rsqrtf((float)dim) / sqrtf(sq + CD_UNIT_EPS), ik = 1.0f / sqrtf(sk + CD_UNIT_EPS);
-    float* vb = p.vbuf + ((size_t)t * p.H + (size_t)g * per) * VP;
-    for (int h = 0; h < per; ++h) {
-        float* r = rec + (size_t)h * PER;
-        const int hh = g * per + h;
-        const float rate = expf(p.A_log[hh]);
-        for (int c = lane; c < DP; c += 32) {
-            float gval = 1.f;
-            if (c < dim) gval = expf(-rate * cd_softplus(p.a[(size_t)t * p.H * dim + hh * dim + c] + p.dt_bias[hh * dim + c]));
-            r[c] = c < dim ? q[c] * iq : 0.f;
-            r[DP + c] = c < dim ? k[c] * ik : 0.f;
-            r[2 * DP + c] = gval;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (warp < ntok) {
+        const float* q = y_all + warp * n_loc;
+        const float* k = q + dim;
+        float sq = 0.f, sk = 0.f, dot = 0.f;
+        for (int c = lane; c < dim; c += 32) {
+            sq += q[c] * q[c];
+            sk += k[c] * k[c];
+            dot += q[c] * k[c];
         }
-        if (lane < 4)
-            r[3 * DP + lane] = lane == 0 ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + hh])) : lane == 1 ? dot * iq * ik : 0.f;
-        for (int c = lane; c < VP; c += 32) vb[(size_t)h * VP + c] = c < vdim ? y[2 * dim + h * vdim + c] : 0.f;
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        dot = warp_sum(dot);
+        if (lane == 0) {
+            const float iq = rsqrtf((float)dim) / sqrtf(sq + CD_UNIT_EPS), ik = 1.0f / sqrtf(sk + CD_UNIT_EPS);
+            stats[warp][0] = iq;
+            stats[warp][1] = ik;
+            stats[warp][2] = dot * iq * ik;
+        }
+    }
+    __syncthreads();
+    // the records of the block's tokens and the group's heads: q | k | g | beta, k.q, 0, 0
+    const int per_rec = 3 * DP + 4;
+    for (int idx = threadIdx.x; idx < ntok * per * per_rec; idx += blockDim.x) {
+        const int tt = idx / (per * per_rec), rem = idx - tt * per * per_rec;
+        const int h = rem / per_rec, e = rem - h * per_rec;
+        const int t = tb + tt, hh = g * per + h;
+        const float* y = y_all + tt * n_loc;
+        float v;
+        if (e < DP) v = e < dim ? y[e] * stats[tt][0] : 0.f;
+        else if (e < 2 * DP) v = e - DP < dim ? y[dim + e - DP] * stats[tt][1] : 0.f;
+        else if (e < 3 * DP) {
+            const int c = e - 2 * DP;
+            v = 1.f;
+            if (c < dim)
+                v = expf(-expf(p.A_log[hh]) * cd_softplus(p.a[(size_t)t * p.H * dim + hh * dim + c] + p.dt_bias[hh * dim + c]));
+        } else {
+            v = e == 3 * DP ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + hh])) : e == 3 * DP + 1 ? stats[tt][2] : 0.f;
+        }
+        p.rec[((size_t)t * p.H + hh) * PER + e] = v;
+    }
+    for (int idx = threadIdx.x; idx < ntok * per * VP; idx += blockDim.x) {
+        const int tt = idx / (per * VP), rem = idx - tt * per * VP;
+        const int h = rem / VP, c = rem - h * VP;
+        p.vbuf[((size_t)(tb + tt) * p.H + g * per + h) * VP + c] = c < vdim ? y_all[tt * n_loc + 2 * dim + h * vdim + c] : 0.f;
     }
 }
 
@@ -264,8 +279,9 @@ static int delta_prep_launch(const DeltaPrepArgs& p, int nt, int B, cudaStream_t
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    dim3 pgrid((nt + CD_PT - 1) / CD_PT, p.G);
-    TB_LAUNCH((delta_prep_kernel<T>), pgrid, 32 * CD_PT, smem, s, p, nt);
+    const int pt = nt >= 256 ? CD_PT : 1;
+    dim3 pgrid((nt + pt - 1) / pt, p.G);
+    TB_LAUNCH((delta_prep_kernel<T>), pgrid, 32 * CD_PT, smem, s, p, nt, pt);
     int rc = tb_last_error();
     if (rc || p.update_state || p.taps == 1) return rc;
     dim3 grid(B, (C + 255) / 256);

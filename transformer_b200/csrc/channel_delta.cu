@@ -124,30 +124,31 @@ __global__ void __launch_bounds__(32 * CD_PT) delta_prep_kernel(const DeltaPrepA
         }
     }
     __syncthreads();
-    // the records of the block's tokens and the group's heads: q | k | g | beta, k.q, 0, 0
-    const int per_rec = 3 * DP + 4;
-    for (int idx = threadIdx.x; idx < ntok * per * per_rec; idx += blockDim.x) {
-        const int tt = idx / (per * per_rec), rem = idx - tt * per * per_rec;
-        const int h = rem / per_rec, e = rem - h * per_rec;
+    // the records of the block's tokens and the group's heads, q | k | g | beta, k.q, 0, 0, and their values: a warp
+    // takes one of the four pieces of a (token, head) at a time
+    for (int u = warp; u < ntok * per * 4; u += blockDim.x >> 5) {
+        const int pair = u >> 2, piece = u & 3;
+        const int tt = pair / per, h = pair - tt * per;
         const int t = tb + tt, hh = g * per + h;
         const float* y = y_all + tt * n_loc;
-        float v;
-        if (e < DP) v = e < dim ? y[e] * stats[tt][0] : 0.f;
-        else if (e < 2 * DP) v = e - DP < dim ? y[dim + e - DP] * stats[tt][1] : 0.f;
-        else if (e < 3 * DP) {
-            const int c = e - 2 * DP;
-            v = 1.f;
-            if (c < dim)
-                v = expf(-expf(p.A_log[hh]) * cd_softplus(p.a[(size_t)t * p.H * dim + hh * dim + c] + p.dt_bias[hh * dim + c]));
+        float* r = p.rec + ((size_t)t * p.H + hh) * PER;
+        if (piece == 0) {
+            const float iq = stats[tt][0];
+            for (int c = lane; c < DP; c += 32) r[c] = c < dim ? y[c] * iq : 0.f;
+        } else if (piece == 1) {
+            const float ik = stats[tt][1];
+            for (int c = lane; c < DP; c += 32) r[DP + c] = c < dim ? y[dim + c] * ik : 0.f;
+        } else if (piece == 2) {
+            const float rate = expf(p.A_log[hh]);
+            const float* a = p.a + (size_t)t * p.H * dim + (size_t)hh * dim;
+            const float* db = p.dt_bias + (size_t)hh * dim;
+            for (int c = lane; c < DP; c += 32) r[2 * DP + c] = c < dim ? expf(-rate * cd_softplus(a[c] + db[c])) : 1.f;
         } else {
-            v = e == 3 * DP ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + hh])) : e == 3 * DP + 1 ? stats[tt][2] : 0.f;
+            if (lane < 4)
+                r[3 * DP + lane] = lane == 0 ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + hh])) : lane == 1 ? stats[tt][2] : 0.f;
+            float* vb = p.vbuf + ((size_t)t * p.H + hh) * VP;
+            for (int c = lane; c < VP; c += 32) vb[c] = c < vdim ? y[2 * dim + h * vdim + c] : 0.f;
         }
-        p.rec[((size_t)t * p.H + hh) * PER + e] = v;
-    }
-    for (int idx = threadIdx.x; idx < ntok * per * VP; idx += blockDim.x) {
-        const int tt = idx / (per * VP), rem = idx - tt * per * VP;
-        const int h = rem / VP, c = rem - h * VP;
-        p.vbuf[((size_t)(tb + tt) * p.H + g * per + h) * VP + c] = c < vdim ? y_all[tt * n_loc + 2 * dim + h * vdim + c] : 0.f;
     }
 }
 

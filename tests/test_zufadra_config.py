@@ -50,6 +50,22 @@ def test_configuration_round_trip_and_what_it_reads():
     assert (meta.bigram.buckets, meta.bigram.mul_prev, meta.bigram.mul_cur) == (37, 31, 7)
 
 
+def test_what_a_configuration_may_leave_out():
+    import copy
+    cfg = copy.deepcopy(T.file_config(T.ONLY_ATTENTION))
+    mix = cfg["layers"][0]["mixer"]
+    heads, dim = mix["heads"], mix["dim"]
+    for k in ("kv_heads", "vdim", "scale", "softcap", "mask"):
+        mix.pop(k, None)
+    mix["rot"]["scaling"] = None
+    cfg["embedding"].pop("bigram")
+    cfg.pop("residual_mult")
+    _, meta = _typed(cfg)
+    a = meta.layers[0].mixer
+    assert (a.kv_heads, a.vdim, a.scale, a.softcap, a.window, a.keep_first) == (heads, dim, dim ** -0.5, 0.0, 0, 0)
+    assert a.rot_scaling is None and meta.bigram is None and meta.residual_mult == 1.0
+
+
 def test_ranks_must_come_from_somewhere():
     arch, meta = _typed(T.file_config(T.ONLY_DELTA))
     with pytest.raises(ConfigError, match="ranks"):

@@ -68,7 +68,10 @@ class AttentionMeta:
             scaling = RotScaling(_num(sc, "factor", w, float), _num(sc, "low", w, float), _num(sc, "high", w, float),
                                  _num(sc, "original", w, float))
         cap = m.get("softcap")
-        return cls(_num(m, "heads", where), _num(m, "kv_heads", where), _num(m, "dim", where), _num(m, "vdim", where),
+        heads, dim = _num(m, "heads", where), _num(m, "dim", where)
+        # what a file may leave out: key heads (as many as query heads), the value size (the key's), the multiplier
+        m = dict(m, kv_heads=m.get("kv_heads", heads), vdim=m.get("vdim", dim), scale=m.get("scale", dim ** -0.5))
+        return cls(heads, _num(m, "kv_heads", where), dim, _num(m, "vdim", where),
                    _num(m, "scale", where, float), 0.0 if cap is None else _num(m, "softcap", where, float),
                    window, keep, _num(rot, "base", where + ".rot", float), _num(rot, "dims", where + ".rot"), scaling)
 
@@ -99,7 +102,9 @@ class DeltaMeta:
     @classmethod
     def from_dict(cls, m, where):
         opt = lambda k: None if m.get(k) is None else _num(m, k, where)
-        return cls(_num(m, "heads", where), _num(m, "kv_heads", where), _num(m, "dim", where), _num(m, "vdim", where),
+        heads, dim = _num(m, "heads", where), _num(m, "dim", where)
+        m = dict(m, kv_heads=m.get("kv_heads", heads), vdim=m.get("vdim", dim))
+        return cls(heads, _num(m, "kv_heads", where), dim, _num(m, "vdim", where),
                    _num(m, "conv", where), opt("decay_rank"), opt("gate_rank"))
 
     def to_dict(self):

@@ -179,16 +179,16 @@ def zufadra_shapes(size):
         "s": (1024, 8, 8, 2, 128, 1024, 64, 2816),
         "m": (2048, 8, 16, 4, 128, 2048, 128, 5632),
     }[size]
-    att = {"heads": H, "kv_heads": G, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+    att = {"heads": H, "kv_heads": G, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
            "mask": {"size": window, "keep_first": 4},
-           "rot": {"base": 1000000.0, "dims": dim // 2,
+           "rot": {"base": 500000.0, "dims": dim // 2,
                    "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     mem = {"heads": H, "kv_heads": H, "dim": dim, "vdim": dim, "conv": 4, "decay_rank": rank, "gate_rank": rank}
     mlp = {"kind": "dense", "ff": ff}
     layers = [{"type": "channel_delta" if i % 2 == 0 else "attention", "mixer": mem if i % 2 == 0 else att, "mlp": mlp}
               for i in range(L)]
-    zufadra = {"architecture": "Zufadra", "vocab": 32000, "width": d, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
-               "logit_scale": 0.25, "embedding": {"scale": 12.0, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+    zufadra = {"architecture": "Zufadra", "vocab": 32000, "width": d, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+               "logit_scale": 0.5, "embedding": {"scale": 8.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
                "max_context": 8192, "layers": layers}
     llama = {"model_type": "llama", "num_hidden_layers": L, "hidden_size": d, "num_attention_heads": H,
              "num_key_value_heads": G, "head_dim": dim, "intermediate_size": ff, "max_position_embeddings": 8192,

@@ -59,12 +59,12 @@ ONLY_DELTA = config(64, 48, [(delta(4, 2, 12, 20, 4, 6, 10), None)], scale=2.0, 
 ONLY_DENSE = config(64, 48, [(delta(1, 1, 8, 8, 2, 4, 4), dense(56))], scale=2.0, logit_scale=0.5, bigram=(64, 1, 1))
 # head sizes the tensor-core kernels take, windows across several pages
 WIDE = config(128, 128, [
-    (attention(4, 2, 64, 64, window=100, keep_first=10, dims=32, scaling=(4.0, 1.0, 4.0, 256), softcap=50.0), dense(96)),
+    (attention(4, 2, 64, 64, window=100, keep_first=10, dims=32, scaling=(3.0, 1.0, 8.0, 256), softcap=40.0), dense(96)),
     (delta(2, 1, 64, 64, 4, 16, 16), None),
-    (attention(8, 2, 128, 128, window=64, keep_first=64, dims=64, base=1e6), dense(96)),
+    (attention(8, 2, 128, 128, window=64, keep_first=64, dims=64, base=5e5), dense(96)),
     (attention(2, 2, 64, 128, window=129, keep_first=1, dims=64), None),
     (delta(2, 2, 128, 128, 4, 16, 16), None),
-], scale=4.0, mult=0.7, logit_scale=0.25, bigram=(509, 127, 17))
+], scale=4.0, mult=0.9, logit_scale=0.75, bigram=(251, 61, 13))
 # sizes that are multiples of nothing: every vectorized or tensor-core form refuses them
 ODD = config(77, 50, [
     (attention(3, 1, 10, 6, window=1, keep_first=3, dims=6, softcap=3.0), dense(22)),

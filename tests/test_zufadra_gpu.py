@@ -472,3 +472,54 @@ def test_stream_sum_without_a_norm(dtype):
         want2 = want.float().double() + u
         assert float((x.cpu().double() - want2).abs().max()) < 1e-5
         assert float((y.cpu().double() - x.cpu().to(td).double()).abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh, nkvh, dk, dv, rdims, half", [(4, 2, 32, 16, 16, 0), (6, 2, 128, 128, 32, 0), (3, 1, 10, 6, 6, 0),
+                                                           (2, 2, 16, 24, 0, 0), (5, 5, 24, 8, 24, 0), (2, 1, 16, 16, 8, 1)])
+def test_norm_over_the_whole_projection_rotation_and_cache_write(dtype, nh, nkvh, dk, dv, rdims, half):
+    """Both forms of the kernel (16-byte accesses where the sizes allow, entry by entry elsewhere): q and k normed over
+    ALL their entries at once, the first ``rdims`` entries of every head turned by the token's angles, q back in
+    place, k and v into the page and row of the token's position."""
+    from transformer_b200.csrc import lib
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    g = torch.Generator().manual_seed(nh * 100 + dk)
+    nt, pad = 5, 8
+    width = (nh + nkvh) * dk + nkvh * dv + pad
+    z = torch.randn(nt, width, generator=g).to(td)
+    qw, kw = torch.rand(nh * dk, generator=g) + 0.5, torch.rand(nkvh * dk, generator=g) + 0.5
+    pos = [0, 63, 64, 130, 7]
+    seq = [0, 1, 2, 3, 4]
+    table = torch.tensor([[3, 0, 0], [5, 0, 0], [1, 2, 0], [4, 6, 7], [0, 0, 0]], dtype=torch.int32)
+    rp = max(rdims // 2, 1)
+    ang = torch.arange(200, dtype=torch.float64)[:, None] * (0.3 ** torch.arange(rp, dtype=torch.float64))[None, :]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    kc = torch.zeros(8, nkvh, 64, dk, dtype=td, device="cuda")
+    vc = torch.zeros(8, nkvh, 64, dv, dtype=td, device="cuda")
+    I = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    d_z, d_qw, d_kw, d_cos, d_sin, d_table, d_seq, d_pos = z.cuda(), qw.cuda(), kw.cuda(), cos.cuda(), sin.cuda(), \
+        table.cuda(), I(seq), I(pos)
+    lib.call("tb_qknorm_rope_cache_" + ("f32" if dtype == "float32" else "bf16"), lib.ptr(d_z), width, lib.ptr(d_qw),
+             lib.ptr(d_kw), 1e-5, lib.ptr(d_seq), lib.ptr(d_pos), lib.ptr(d_table), 3, lib.ptr(d_cos), lib.ptr(d_sin),
+             lib.ptr(kc), lib.ptr(vc), nt, nh, nkvh, dk, dv, rdims, half)
+    torch.cuda.synchronize()
+    zd = z.double()
+    nq, nk = nh * dk, nkvh * dk
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    for t in range(nt):
+        q = ZP.rms_norm(zd[t, :nq], qw.double(), 1e-5).view(nh, dk)
+        k = ZP.rms_norm(zd[t, nq:nq + nk], kw.double(), 1e-5).view(nkvh, dk)
+
+        def turn(x):
+            y = x.clone()
+            for i in range(rdims // 2):
+                i0, i1 = (i, i + rdims // 2) if half else (2 * i, 2 * i + 1)
+                c, s = cos[pos[t], i].double(), sin[pos[t], i].double()
+                y[:, i0] = x[:, i0] * c - x[:, i1] * s
+                y[:, i1] = x[:, i1] * c + x[:, i0] * s
+            return y
+        page, r = int(table[t, pos[t] // 64]), pos[t] % 64
+        assert float((d_z[t, :nq].cpu().double() - turn(q).reshape(-1)).abs().max()) <= tol
+        assert float((kc[page, :, r].cpu().double() - turn(k)).abs().max()) <= tol
+        assert torch.equal(vc[page, :, r].cpu(), z[t, nq + nk:nq + nk + nkvh * dv].view(nkvh, dv))
+        assert torch.equal(d_z[t, nq:].cpu(), z[t, nq:])          # k, v and what lies behind them stay as they were

@@ -260,6 +260,88 @@ qknorm_rope_cache_kernel(T* __restrict__ z, int ldz, const float* __restrict__ q
         }
 }
 
+// The same, eight entries at a time with 16-byte accesses: head sizes, the rotated part and the row pitch multiples
+// of eight, adjacent pairs.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qknorm_rope_cache_vec_kernel(T* __restrict__ z, int ldz, const float* __restrict__ q_norm,
+                             const float* __restrict__ k_norm, float eps, const int* __restrict__ tok_seq,
+                             const int* __restrict__ tok_pos, const int* __restrict__ page_table, int max_pages,
+                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, T* __restrict__ kc,
+                             T* __restrict__ vc, int nh, int nkvh, int dk, int dv, int rdims) {
+    pdl_sync();
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int nq = nh * dk, nk = nkvh * dk;
+    T* row = z + (size_t)t * ldz;
+    float rq = 1.f, rk = 1.f;
+    if (q_norm) {
+        float ss = 0.f;
+        for (int c = threadIdx.x * 8; c < nq; c += blockDim.x * 8) {
+            float x[8];
+            load8(row + c, x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+        }
+        rq = 1.0f / sqrtf(block_sum(ss, red) / (float)nq + eps);
+    }
+    if (k_norm) {
+        float ss = 0.f;
+        for (int c = threadIdx.x * 8; c < nk; c += blockDim.x * 8) {
+            float x[8];
+            load8(row + nq + c, x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+        }
+        rk = 1.0f / sqrtf(block_sum(ss, red) / (float)nk + eps);
+    }
+    const int rp = rdims >> 1;
+    const float* cs = cos_t + (size_t)pos * rp;
+    const float* sn = sin_t + (size_t)pos * rp;
+    size_t cache_row = 0;
+    if (kc) {
+        const int page = page_table[(size_t)tok_seq[t] * max_pages + pos / TB_PAGE];
+        cache_row = (size_t)page * nkvh * TB_PAGE + (pos % TB_PAGE);
+    }
+    for (int c = threadIdx.x * 8; c < nq + nk; c += blockDim.x * 8) {
+        const bool is_q = c < nq;
+        const int head = c / dk, within = c - head * dk;          // q and k heads are adjacent and equally wide
+        const float* w = is_q ? q_norm : k_norm;
+        const float r = is_q ? rq : rk;
+        float x[8], y[8];
+        load8(row + c, x);
+        if (w) {
+            float wv[8];
+            load8(w + (is_q ? c : c - nq), wv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[e] *= r * wv[e];
+        }
+        if (within < rdims) {           // four pairs, angles within / 2 .. within / 2 + 3
+            const float4 c4 = *reinterpret_cast<const float4*>(cs + (within >> 1));
+            const float4 s4 = *reinterpret_cast<const float4*>(sn + (within >> 1));
+            const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                y[2 * e] = x[2 * e] * cc[e] - x[2 * e + 1] * ss[e];
+                y[2 * e + 1] = x[2 * e + 1] * cc[e] + x[2 * e] * ss[e];
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = x[e];
+        }
+        if (is_q) store8(row + c, y);
+        else if (kc) store8(kc + (cache_row + (size_t)(head - nh) * TB_PAGE) * dk + within, y);
+    }
+    if (vc)
+        for (int c = threadIdx.x * 8; c < nkvh * dv; c += blockDim.x * 8) {
+            const int head = c / dv, within = c - head * dv;
+            float x[8];
+            load8(row + nq + nk + c, x);
+            store8(vc + (cache_row + (size_t)head * TB_PAGE) * dv + within, x);
+        }
+}
+
 template <typename T>
 static int qknorm_rope_cache_launch(void* z, int ldz, const float* q_norm, const float* k_norm, float eps,
                                     const int* tok_seq, const int* tok_pos, const int* page_table, int max_pages,
@@ -268,6 +350,13 @@ static int qknorm_rope_cache_launch(void* z, int ldz, const float* q_norm, const
     if (nt < 0 || nh <= 0 || nkvh <= 0 || dk <= 0 || dv <= 0 || rdims < 0 || rdims > dk || (rdims & 1)) return TB_ERR_ARG;
     if ((kc == nullptr) != (vc == nullptr) || ldz < (nh + nkvh) * dk + nkvh * dv) return TB_ERR_ARG;
     if (nt == 0) return 0;
+    if (!half_pairing && dk % 8 == 0 && dv % 8 == 0 && rdims % 8 == 0 && ldz % 8 == 0 &&
+        (((uintptr_t)z | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)q_norm | (uintptr_t)k_norm | (uintptr_t)cos_t |
+          (uintptr_t)sin_t) & 15) == 0) {
+        TB_LAUNCH((qknorm_rope_cache_vec_kernel<T>), nt, 256, 0, s, (T*)z, ldz, q_norm, k_norm, eps, tok_seq, tok_pos,
+                  page_table, max_pages, cos_t, sin_t, (T*)kc, (T*)vc, nh, nkvh, dk, dv, rdims);
+        return tb_last_error();
+    }
     TB_LAUNCH((qknorm_rope_cache_kernel<T>), nt, 256, 0, s, (T*)z, ldz, q_norm, k_norm, eps, tok_seq, tok_pos, page_table,
               max_pages, cos_t, sin_t, (T*)kc, (T*)vc, nh, nkvh, dk, dv, rdims, half_pairing);
     return tb_last_error();

@@ -227,7 +227,10 @@ __global__ void __launch_bounds__(CD_THREADS) delta_scan_kernel(const DeltaScanA
         __syncthreads();            // this stage has landed for everyone, and everyone is done with the stage before
         if (ts + CD_TOK < t1) issue(ts + CD_TOK, par ^ 1);
         const int ntok = min(CD_TOK, t1 - ts);
-        for (int tt = 0; tt < ntok; ++tt) {
+        float* o_tok = a.out + ((size_t)ts * H + h) * vdim + col;        // this thread's output of the stage's first token
+#pragma unroll
+        for (int tt = 0; tt < CD_TOK; ++tt) {
+            if (tt >= ntok) break;
             const float* row = &sm[par][tt][0];
             const float4* Q4 = reinterpret_cast<const float4*>(row);
             const float4* K4 = reinterpret_cast<const float4*>(row + DP);
@@ -256,7 +259,7 @@ __global__ void __launch_bounds__(CD_THREADS) delta_scan_kernel(const DeltaScanA
                 float* si = s + i4 * 4;
                 si[0] += kk[i4].x * u; si[1] += kk[i4].y * u; si[2] += kk[i4].z * u; si[3] += kk[i4].w * u;
             }
-            if (part == 0 && has_col) a.out[((size_t)(ts + tt) * H + h) * vdim + col] = sq + u * row[3 * DP + 1];
+            if (part == 0 && has_col) o_tok[(size_t)tt * H * vdim] = sq + u * row[3 * DP + 1];
         }
     }
 #pragma unroll
